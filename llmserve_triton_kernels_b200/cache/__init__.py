@@ -6,9 +6,9 @@ def num_pages_for_budget(cache_specs, page_size: int, element_size: int, budget_
     """How many pages each group gets when ``budget_bytes`` is shared by all of them
     (src/llmserve/kvcache/paged.py:221-227: bytes of one page = 2 * layers * kv_heads * page_size *
     head_dim * element size)."""
-    from ..parts.base import PagedKVSpec
+    from ..parts.base import PagedKVSpec, PagedRowSpec
 
     per_page = sum(
         2 * s.kv_heads * page_size * s.head_dim * element_size for s in cache_specs if isinstance(s, PagedKVSpec)
-    )
+    ) + sum(s.width * page_size * element_size for s in cache_specs if isinstance(s, PagedRowSpec))
     return max(1, budget_bytes // per_page) if per_page else 1

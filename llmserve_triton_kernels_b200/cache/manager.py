@@ -23,7 +23,7 @@ from dataclasses import dataclass
 import numpy as np
 import torch
 
-from ..parts.base import PagedKVSpec, StateSpec
+from ..parts.base import PagedKVSpec, PagedRowSpec, StateSpec
 from .allocator import IdAllocator, OutOfPages
 
 RELEASED = -1  # table entry of a page that a window has passed
@@ -33,11 +33,11 @@ RELEASED = -1  # table entry of a page that a window has passed
 class PagedKVView:
     """What an attention layer sees of its cache in one step."""
 
-    pool: torch.Tensor  # [pages, 2, kv_heads, page_size, head_dim]: this entry's plane
+    pool: torch.Tensor  # this entry's plane: [pages, 2, kv_heads, page_size, head_dim], or [pages, page_size, width] for rows
     page_table: torch.Tensor  # [requests, width] int32, physical page of each logical page
     slot_map: torch.Tensor  # [tokens] int32: page * page_size + offset of each new token
     page_size: int
-    spec: PagedKVSpec
+    spec: PagedKVSpec | PagedRowSpec
 
 
 @dataclass
@@ -55,11 +55,14 @@ class PageGroup:
         self.entries = entries  # positions in the model's order that own a plane here
         self.num_pages = int(num_pages)
         self.page_size = int(page_size)
-        self.pool = torch.zeros(
-            (len(entries), self.num_pages, 2, spec.kv_heads, self.page_size, spec.head_dim),
-            dtype=dtype,
-            device=device,
-        )
+        # what one token place of one plane holds: keys and values of every head, or one row
+        if isinstance(spec, PagedRowSpec):
+            self.place_elements = spec.width
+            shape = (len(entries), self.num_pages, self.page_size, spec.width)
+        else:
+            self.place_elements = 2 * spec.kv_heads * spec.head_dim
+            shape = (len(entries), self.num_pages, 2, spec.kv_heads, self.page_size, spec.head_dim)
+        self.pool = torch.zeros(shape, dtype=dtype, device=device)
         self.allocator = IdAllocator(self.num_pages, "page")
         self.tables: dict[object, list[int]] = {}
         # the same tables as int32 arrays with room to grow (released pages as 0), so that a step's table is put
@@ -102,7 +105,7 @@ class PageGroup:
         return max(0, last + 1 - len(table))
 
     def bytes_per_page(self) -> int:
-        return len(self.entries) * 2 * self.spec.kv_heads * self.page_size * self.spec.head_dim * self.pool.element_size()
+        return len(self.entries) * self.place_elements * self.page_size * self.pool.element_size()
 
 
 class CacheManager:
@@ -127,10 +130,10 @@ class CacheManager:
         self.schedule = list(schedule)
         self.groups: list[PageGroup] = []
         self._entry_group: dict[int, tuple[int, int]] = {}  # order entry -> (group, plane)
-        by_spec: dict[PagedKVSpec, list[int]] = {}
+        by_spec: dict[PagedKVSpec | PagedRowSpec, list[int]] = {}
         self._state_entries: dict[int, torch.Tensor] = {}
         for i, spec in enumerate(cache_specs):
-            if isinstance(spec, PagedKVSpec):
+            if isinstance(spec, (PagedKVSpec, PagedRowSpec)):
                 by_spec.setdefault(spec, []).append(i)
             elif isinstance(spec, StateSpec):
                 self._state_entries[i] = torch.zeros(
@@ -245,6 +248,10 @@ class CacheManager:
                 g.allocator.free([table[i] for i in stale])
                 for i in stale:
                     g.release_page(req, i)
+
+    def position_limit(self, model_limit: int | None) -> int:
+        """The most tokens a request may hold: the model's limit; for a model without one, what the pool has room for."""
+        return int(model_limit) if model_limit else max(1, self.num_pages * self.page_size)
 
     def reset(self) -> None:
         for req in list(self.lengths):

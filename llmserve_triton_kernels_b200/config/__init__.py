@@ -1,4 +1,5 @@
 from .llama import ConfigError, LlamaConfig  # noqa: F401
+from .nurolorn import NurolornConfig  # noqa: F401
 from .registry import (  # noqa: F401
     Architecture,
     architecture_of,

@@ -50,11 +50,15 @@ def get_architecture(name: str) -> Architecture:
 
 
 def architecture_of(config_dict: dict) -> Architecture:
+    """By config.json's ``architectures`` list (its first entry) or, where a design writes it so, its ``architecture``
+    string."""
     names = config_dict.get("architectures")
+    if not names and isinstance(config_dict.get("architecture"), str):
+        names = [config_dict["architecture"]]
     if not names or not isinstance(names, (list, tuple)):
         raise KeyError(
-            "config.json has no 'architectures' list, so the model class cannot be chosen; "
-            f"known architectures: {known_architectures()}"
+            "config.json has neither an 'architectures' list nor an 'architecture' name, so the model class cannot be "
+            f"chosen; known architectures: {known_architectures()}"
         )
     return get_architecture(names[0])
 

@@ -1,4 +1,4 @@
-// Paged grouped-query attention for any mix of query lengths, any head size up to 256 and any
+// Paged attention for any mix of query lengths, any key size up to 640 lanes, any value size up to 512 and any
 // group size: one warp per (token, query head).
 //
 // This is the attention of the true 32-bit path and the fallback of the bfloat16 path for
@@ -7,41 +7,62 @@
 // the absolute key position, so the order of every addition depends only on the query's
 // position (and the window), never on how the tokens were cut into steps or batched.
 //
-// q rows hold the query heads first (row stride q_stride elements); out is [tokens, H * D].
-// pool plane: [pages, 2, KV, page_size, D].  A query at position p of request r sees keys
-// max(0, p - window + 1) .. p (window <= 0: from 0).
+// A query at position p of request r sees keys max(0, p - window + 1) .. p (window <= 0: from 0).
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace {
 
 constexpr int WARPS = 4;
-constexpr int MAX_D = 256;
+constexpr int MAX_DK = 640;  // most lanes of a query and a key
+constexpr int MAX_DV = 512;  // most lanes of a value
+
+// Where queries, keys and values lie.  A query is one or two runs of lanes (the second may be absent): run 0 holds
+// lanes [0, d0), run 1 lanes [d0, d0 + d1); each run is addressed by a token stride and a head stride.  Keys and
+// values are addressed by page, key/value head and place in the page; values may be the first dv lanes of the keys
+// (the same pointer and strides).
+template <typename T>
+struct RowsArgs {
+    const T *q0, *q1;
+    long long q0_token, q0_head, q1_token, q1_head;
+    int d0, d1;
+    T* out;
+    long long out_token, out_head;
+    const T *keys, *values;
+    long long k_page, k_head, k_token, v_page, v_head, v_token;
+    int dv;
+    const int *page_table, *token_request, *cu_tokens, *ctx_lens;
+    const float* slopes;  // per query head: the score of key j for the query at position i loses slope * (i - j); null: none
+    int table_width, n_tokens, H, KV, page_size, window;
+    float scale;
+};
 
 template <typename T>
-__global__ void __launch_bounds__(WARPS * 32)
-attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
-                         const T* __restrict__ pool, const int* __restrict__ page_table, int table_width,
-                         const int* __restrict__ token_request, const int* __restrict__ cu_tokens,
-                         const int* __restrict__ ctx_lens, int n_tokens, int H, int KV, int D, int page_size,
-                         int window, float scale) {
-    __shared__ float q_s[WARPS][MAX_D];
+__global__ void __launch_bounds__(WARPS * 32) attention_rows_kernel(const RowsArgs<T> a) {
+    __shared__ float q_s[WARPS][MAX_DK];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * WARPS + warp;
-    if (item >= (long long)n_tokens * H) return;
-    const int t = (int)(item / H), h = (int)(item - (long long)t * H);
-    const int r = token_request[t];
-    const int q_begin = cu_tokens[r], q_len = cu_tokens[r + 1] - q_begin;
-    const int pos = ctx_lens[r] - q_len + (t - q_begin);
-    const int kvh = h / (H / KV);
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (item >= (long long)a.n_tokens * a.H) return;
+    const int t = (int)(item / a.H), h = (int)(item - (long long)t * a.H);
+    const int r = a.token_request[t];
+    const int q_begin = a.cu_tokens[r], q_len = a.cu_tokens[r + 1] - q_begin;
+    const int pos = a.ctx_lens[r] - q_len + (t - q_begin);
+    const int kvh = h / (a.H / a.KV);
+    const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    const int dk = a.d0 + a.d1, dv = a.dv;
+    const float slope = a.slopes ? a.slopes[h] : 0.f;
 
-    const T* qp = q + (size_t)t * q_stride + (size_t)h * D;
-    for (int d = lane; d < D; d += 32) q_s[warp][d] = to_float(qp[d]);
+    const T* qp = a.q0 + (long long)t * a.q0_token + (long long)h * a.q0_head;
+    for (int d = lane; d < a.d0; d += 32) q_s[warp][d] = to_float(qp[d]);
+    if (a.d1 > 0) {
+        const T* qr = a.q1 + (long long)t * a.q1_token + (long long)h * a.q1_head;
+        for (int d = lane; d < a.d1; d += 32) q_s[warp][a.d0 + d] = to_float(qr[d]);
+    }
     __syncwarp();
 
-    const int* table = page_table + (size_t)r * table_width;
-    const size_t head_stride = (size_t)page_size * D;
-    constexpr int ACC = MAX_D / 32;
+    const int* table = a.page_table + (size_t)r * a.table_width;
+    constexpr int ACC = MAX_DV / 32;
     float acc[ACC];
 #pragma unroll
     for (int i = 0; i < ACC; ++i) acc[i] = 0.f;
@@ -52,11 +73,11 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
         const bool visible = j >= lo && j <= pos;
         float s = -INFINITY;
         if (visible) {
-            const int page = table[j / page_size], off = j % page_size;
-            const T* kp = pool + ((size_t)(page * 2 + 0) * KV + kvh) * head_stride + (size_t)off * D;
+            const int page = table[j / a.page_size], off = j % a.page_size;
+            const T* kp = a.keys + (long long)page * a.k_page + (long long)kvh * a.k_head + (long long)off * a.k_token;
             float dot = 0.f;
-            for (int d = 0; d < D; ++d) dot = fmaf(q_s[warp][d], to_float(kp[d]), dot);
-            s = dot * scale;
+            for (int d = 0; d < dk; ++d) dot = fmaf(q_s[warp][d], to_float(kp[d]), dot);
+            s = dot * a.scale - slope * (float)(pos - j);
         }
         const float m_new = fmaxf(m, warp_max(s));  // finite: the chunk holds at least one visible key
         const float p = visible ? expf(s - m_new) : 0.f;
@@ -70,45 +91,87 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             if (pj == 0.f) continue;  // uniform across the warp
             const int key = c + jj;
-            const int page = table[key / page_size], off = key % page_size;
-            const T* vp = pool + ((size_t)(page * 2 + 1) * KV + kvh) * head_stride + (size_t)off * D;
+            const int page = table[key / a.page_size], off = key % a.page_size;
+            const T* vp = a.values + (long long)page * a.v_page + (long long)kvh * a.v_head + (long long)off * a.v_token;
 #pragma unroll
             for (int i = 0; i < ACC; ++i) {
                 const int d = lane + 32 * i;
-                if (d < D) acc[i] = fmaf(pj, to_float(vp[d]), acc[i]);
+                if (d < dv) acc[i] = fmaf(pj, to_float(vp[d]), acc[i]);
             }
         }
     }
     const float inv = 1.f / l;
-    T* op = out + (size_t)t * out_stride + (size_t)h * D;
+    T* op = a.out + (long long)t * a.out_token + (long long)h * a.out_head;
 #pragma unroll
     for (int i = 0; i < ACC; ++i) {
         const int d = lane + 32 * i;
-        if (d < D) op[d] = from_float<T>(acc[i] * inv);
+        if (d < dv) op[d] = from_float<T>(acc[i] * inv);
     }
+}
+
+template <typename T>
+int launch_rows(const RowsArgs<T>& a, cudaStream_t stream) {
+    const long long items = (long long)a.n_tokens * a.H;
+    const long long blocks = (items + WARPS - 1) / WARPS;
+    if (blocks > 0x7fffffffLL) return LLM_ERR_UNSUPPORTED;
+    attention_rows_kernel<T><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(a);
+    return launch_status();
 }
 
 }  // namespace
 
+// Queries in two runs of lanes, keys and values by strides, an optional distance bias per head: the form that
+// attention with other key than value sizes, and attention over a latent that is key and value at once, come in.
+LLM_EXPORT int llm_attention_rows(const void* q0, long long q0_token, long long q0_head, int d0, const void* q1,
+                                  long long q1_token, long long q1_head, int d1, void* out, long long out_token,
+                                  long long out_head, const void* keys, long long k_page, long long k_head, long long k_token,
+                                  const void* values, long long v_page, long long v_head, long long v_token, int dv, int dtype,
+                                  const int* page_table, int table_width, const int* token_request, const int* cu_tokens,
+                                  const int* ctx_lens, const float* slopes, int n_tokens, int H, int KV, int page_size,
+                                  int window, float scale, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (d0 <= 0 || d1 < 0 || d0 + d1 > MAX_DK || dv <= 0 || dv > MAX_DV || H <= 0 || KV <= 0 || H % KV || page_size <= 0 ||
+        table_width <= 0 || (d1 > 0 && q1 == nullptr))
+        return LLM_ERR_BAD_ARGUMENT;
+    auto fill = [&](auto& a, auto* tag) {
+        using T = std::remove_pointer_t<decltype(tag)>;
+        a.q0 = (const T*)q0; a.q1 = (const T*)q1;
+        a.q0_token = q0_token; a.q0_head = q0_head; a.q1_token = q1_token; a.q1_head = q1_head;
+        a.d0 = d0; a.d1 = d1;
+        a.out = (T*)out; a.out_token = out_token; a.out_head = out_head;
+        a.keys = (const T*)keys; a.values = (const T*)values;
+        a.k_page = k_page; a.k_head = k_head; a.k_token = k_token; a.v_page = v_page; a.v_head = v_head; a.v_token = v_token;
+        a.dv = dv;
+        a.page_table = page_table; a.token_request = token_request; a.cu_tokens = cu_tokens; a.ctx_lens = ctx_lens;
+        a.slopes = slopes;
+        a.table_width = table_width; a.n_tokens = n_tokens; a.H = H; a.KV = KV; a.page_size = page_size; a.window = window;
+        a.scale = scale;
+    };
+    if (dtype == LLM_F32) {
+        RowsArgs<float> a;
+        fill(a, (float*)nullptr);
+        return launch_rows(a, stream);
+    }
+    if (dtype == LLM_BF16) {
+        RowsArgs<__nv_bfloat16> a;
+        fill(a, (__nv_bfloat16*)nullptr);
+        return launch_rows(a, stream);
+    }
+    return LLM_ERR_BAD_ARGUMENT;
+}
+
+// Queries of one run at the head of their rows, keys and values of one size D in a pool plane [pages, 2, KV, page_size, D].
 LLM_EXPORT int llm_attention_generic(const void* q, int q_stride, void* out, int out_stride, const void* pool,
                                      int dtype, const int* page_table, int table_width, const int* token_request,
                                      const int* cu_tokens, const int* ctx_lens, int n_tokens, int H, int KV, int D,
                                      int page_size, int window, float scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (D <= 0 || D > MAX_D || H <= 0 || KV <= 0 || H % KV || page_size <= 0 || table_width <= 0)
+    if (D <= 0 || D > 256 || H <= 0 || KV <= 0 || H % KV || page_size <= 0 || table_width <= 0)
         return LLM_ERR_BAD_ARGUMENT;
-    const long long items = (long long)n_tokens * H;
-    const long long blocks = (items + WARPS - 1) / WARPS;
-    if (blocks > 0x7fffffffLL) return LLM_ERR_UNSUPPORTED;
-    if (dtype == LLM_F32)
-        attention_generic_kernel<float><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(
-            (const float*)q, q_stride, (float*)out, out_stride, (const float*)pool, page_table, table_width,
-            token_request, cu_tokens, ctx_lens, n_tokens, H, KV, D, page_size, window, scale);
-    else if (dtype == LLM_BF16)
-        attention_generic_kernel<__nv_bfloat16><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(
-            (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)pool, page_table,
-            table_width, token_request, cu_tokens, ctx_lens, n_tokens, H, KV, D, page_size, window, scale);
-    else
-        return LLM_ERR_BAD_ARGUMENT;
-    return launch_status();
+    const long long head = (long long)page_size * D, page = 2LL * KV * head;
+    const size_t element = dtype == LLM_F32 ? 4 : 2;
+    const void* values = (const char*)pool + (size_t)KV * head * element;
+    return llm_attention_rows(q, q_stride, D, D, nullptr, 0, 0, 0, out, out_stride, D, pool, page, head, D, values, page, head,
+                              D, D, dtype, page_table, table_width, token_request, cu_tokens, ctx_lens, nullptr, n_tokens, H,
+                              KV, page_size, window, scale, stream);
 }

@@ -13,7 +13,10 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4, THREADS = 256;
 template <typename TX, typename TW, typename TO>
 __global__ void __launch_bounds__(THREADS)
 gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out, int M, int N, int K,
-                 int ldx, int ldw, int ldo) {
+                 int ldx, int ldw, int ldo, long long x_batch, long long w_batch, long long o_batch) {
+    x += (long long)blockIdx.z * x_batch;  // one product per z: operands and result a fixed stride apart
+    w += (long long)blockIdx.z * w_batch;
+    out += (long long)blockIdx.z * o_batch;
     __shared__ float xs[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -75,10 +78,10 @@ gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __restr
 
 template <typename TX, typename TW, typename TO>
 int launch(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldw, int ldo,
-           cudaStream_t stream) {
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+           cudaStream_t stream, int batches = 1, long long x_batch = 0, long long w_batch = 0, long long o_batch = 0) {
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batches);
     gemm_simt_kernel<TX, TW, TO><<<grid, THREADS, 0, stream>>>((const TX*)x, (const TW*)w, (TO*)out, M, N, K, ldx,
-                                                               ldw, ldo);
+                                                               ldw, ldo, x_batch, w_batch, o_batch);
     return launch_status();
 }
 
@@ -96,5 +99,23 @@ LLM_EXPORT int llm_gemm_simt(const void* x, int x_dtype, const void* w, int w_dt
         return launch<bf, bf, bf>(x, w, out, M, N, K, ldx, ldw, ldo, stream);
     if (x_dtype == LLM_BF16 && w_dtype == LLM_BF16 && out_dtype == LLM_F32)
         return launch<bf, bf, float>(x, w, out, M, N, K, ldx, ldw, ldo, stream);
+    return LLM_ERR_BAD_ARGUMENT;
+}
+
+// `batches` products of one shape: product b reads x + b * x_batch and w + b * w_batch (in elements) and writes
+// out + b * o_batch.  Heads that lie side by side in a row are batches with a stride of one head.
+LLM_EXPORT int llm_gemm_simt_batched(const void* x, const void* w, void* out, int dtype, int out_dtype, int M, int N, int K,
+                                     int ldx, int ldw, int ldo, int batches, long long x_batch, long long w_batch,
+                                     long long o_batch, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batches <= 0) return 0;
+    if (K < 0 || ldx < K || ldw < K || ldo < N) return LLM_ERR_BAD_ARGUMENT;
+    if ((M + BM - 1) / BM > 65535 || batches > 65535) return LLM_ERR_UNSUPPORTED;
+    using bf = __nv_bfloat16;
+    if (dtype == LLM_F32 && out_dtype == LLM_F32)
+        return launch<float, float, float>(x, w, out, M, N, K, ldx, ldw, ldo, stream, batches, x_batch, w_batch, o_batch);
+    if (dtype == LLM_BF16 && out_dtype == LLM_BF16)
+        return launch<bf, bf, bf>(x, w, out, M, N, K, ldx, ldw, ldo, stream, batches, x_batch, w_batch, o_batch);
+    if (dtype == LLM_BF16 && out_dtype == LLM_F32)
+        return launch<bf, bf, float>(x, w, out, M, N, K, ldx, ldw, ldo, stream, batches, x_batch, w_batch, o_batch);
     return LLM_ERR_BAD_ARGUMENT;
 }

@@ -46,7 +46,8 @@ class StepGraph:
                 if not 0 <= w < self.counts[r]:
                     raise ValueError(f"place {w} is wanted among {self.counts[r]} tokens")
         P = len(rows)
-        self.widths = [-(-model.plan.max_positions // g.page_size) for g in cache.groups]
+        self.max_positions = cache.position_limit(model.plan.max_positions)
+        self.widths = [-(-self.max_positions // g.page_size) for g in cache.groups]
         sizes = [N, N, N, R + 1, R, P, R]  # ids, positions, token_request, cu, ctx_lens, logit_rows, state_slots
         for w in self.widths:
             sizes += [R * w, N]
@@ -71,7 +72,7 @@ class StepGraph:
             num_tokens=N, num_requests=R, num_logits=P,
             token_ids=d(0), positions=d(1), token_request=d(2), cu_tokens=d(3), context_lens=d(4), logit_rows=d(5),
             state_slots=d(6), host_cu_tokens=cu.tolist(), host_context_lens=None, host_state_slots=None,
-            max_query_len=max(self.counts), max_context_len=model.plan.max_positions, static_decode=self.decode_only,
+            max_query_len=max(self.counts), max_context_len=self.max_positions, static_decode=self.decode_only,
         )
         group_tensors = []
         for g, w in enumerate(self.widths):

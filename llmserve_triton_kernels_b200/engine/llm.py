@@ -22,7 +22,7 @@ from ..cache import CacheManager, num_pages_for_budget
 from ..config.presets import PRESETS
 from ..config.registry import architecture_of
 from ..models.load import load_model, random_model, resolve_dtype
-from ..parts.base import PagedKVSpec
+from ..parts.base import PagedKVSpec, PagedRowSpec
 from ..sampling import Sampler, SamplingParams
 from .scheduler import Scheduler
 from .step import StepFunction
@@ -84,16 +84,19 @@ class LLM:
                 tokenizer = _maybe_tokenizer(model)
         self.tokenizer = tokenizer
         specs = self.model.cache_specs()
+        # a model without a position limit of its own: a request may be as long as the scheduler's token budget
+        # allows it to be taken in, and the pool is sized for that
+        model_limit = self.model.plan.max_positions or max(max_num_batched_tokens, 2048)
         element = torch.empty(0, dtype=self.dtype).element_size()
         if num_blocks is None:
             if kv_mem_mib is not None:
                 num_blocks = num_pages_for_budget(specs, block_size, element, int(kv_mem_mib * 2**20))
             else:  # room for every request slot at the model's full length, within a quarter of the free memory
-                want = max_batch_size * -(-self.model.plan.max_positions // block_size)
+                want = max_batch_size * -(-model_limit // block_size)
                 cap = want
                 if self.device.type == "cuda":
                     free, _ = torch.cuda.mem_get_info(self.device)
-                    groups = {s for s in specs if isinstance(s, PagedKVSpec)}
+                    groups = {s for s in specs if isinstance(s, (PagedKVSpec, PagedRowSpec))}
                     cap = num_pages_for_budget(specs, block_size, element, free // 4) // max(1, len(groups))
                 num_blocks = max(1, min(want, cap))
         self.cache = CacheManager(
@@ -103,7 +106,7 @@ class LLM:
         self.step_function = StepFunction(self.model, self.cache)
         self.sampler = Sampler(self.device)
         self.scheduler = Scheduler(
-            self.step_function, self.cache, self.sampler, max_position=self.model.plan.max_positions,
+            self.step_function, self.cache, self.sampler, max_position=self.step_function.max_positions,
             max_batch_size=max_batch_size, max_num_batched_tokens=max_num_batched_tokens, chunk_size=chunk_size,
             policy=policy,
         )

@@ -29,6 +29,8 @@ class StepFunction:
         device, when every part of the model says it can be captured)."""
         self.model = model
         self.cache = cache
+        # the most tokens a request may hold: the model's own limit, or what the cache has room for
+        self.max_positions = cache.position_limit(model.plan.max_positions)
         self.h2d_bytes = 0  # bytes of the last step's descriptor copy
         self.last_context: StepContext | None = None
         if use_graphs is None:
@@ -46,7 +48,7 @@ class StepFunction:
         overwrites: read or copy it before stepping again."""
         if not entries:
             raise ValueError("a step needs at least one entry")
-        cache, limit = self.cache, self.model.plan.max_positions
+        cache, limit = self.cache, self.max_positions
         vocab = self.model.plan.vocab_size
         pairs = []
         for e in entries:
@@ -120,7 +122,7 @@ class StepFunction:
         never reads the tokens here; elsewhere this is an ordinary step on tokens read from the tensor."""
         if not self.use_graphs:  # no graphs (a model that cannot be captured, or the CPU under test): the plain way
             return self([StepEntry(r, [int(t)], [0]) for r, t in zip(requests, device_tokens.tolist())])
-        cache, limit = self.cache, self.model.plan.max_positions
+        cache, limit = self.cache, self.max_positions
         for r in requests:
             if cache.lengths[r] + 1 > limit:
                 raise ValueError(f"request {r!r} would hold {cache.lengths[r] + 1} tokens, beyond the model's {limit} positions")

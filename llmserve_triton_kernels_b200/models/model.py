@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from ..parts.base import Block, PagedKVSpec, StateSpec, TensorSpec, build_part, part_factory
+from ..parts.base import Block, PagedKVSpec, PagedRowSpec, StateSpec, TensorSpec, build_part, part_factory
 from .plan import ModelPlan
 
 
@@ -44,6 +44,11 @@ class Model:
         self._named_parts.append((plan.final_norm.prefix, self.final_norm))
         self.embedding: torch.Tensor | None = None
         self.head: torch.Tensor | None = None
+        self._injections = {inj.before: inj for inj in plan.injections}
+        self._vectors: dict[str, torch.Tensor] = {}  # the plan's extra tensors, 32-bit
+        # a function (entry index, residual stream [N, hidden] with everything added) that is called after every
+        # entry of the order when it is set: for looking at the stream layer by layer (it costs a copy per layer)
+        self.layer_probe = None
 
     # ------------------------------------------------------------------ tensors
     def tensor_specs(self) -> dict[str, TensorSpec]:
@@ -58,6 +63,10 @@ class Model:
                 specs[name] = spec
         if plan.head is not None:
             specs[plan.head] = TensorSpec((plan.vocab_size, plan.hidden_size))
+        for name, shape in plan.extra_tensors:
+            if name in specs:
+                raise ValueError(f"two owners claim the tensor {name!r}")
+            specs[name] = TensorSpec(tuple(shape))
         return specs
 
     def ignored_tensor_names(self) -> set[str]:
@@ -74,6 +83,8 @@ class Model:
         for prefix, part in self._named_parts:
             local = {name: tensors[prefix + name] for name in part.tensors()}
             part.bind(local, self.dtype, self.device)
+        for name, _ in plan.extra_tensors:
+            self._vectors[name] = tensors[name].to(device=self.device, dtype=torch.float32).contiguous()
 
     def weight_bytes(self) -> int:
         """Bytes of every distinct weight tensor a step reads (the token table only if it is also the head)."""
@@ -99,7 +110,7 @@ class Model:
         ) and getattr(self.final_norm, "graph_safe", False)
 
     # ------------------------------------------------------------------ caches
-    def cache_specs(self) -> list[PagedKVSpec | StateSpec | None]:
+    def cache_specs(self) -> list[PagedKVSpec | PagedRowSpec | StateSpec | None]:
         """For each entry of the order: what its mixer keeps, or None if it keeps nothing of its
         own (no cache, or it reads an earlier entry's)."""
         out = []
@@ -117,18 +128,39 @@ class Model:
         pending = None
         order = self.plan.schedule
         for i, run in enumerate(order):
-            # the norm that meets the stream next, so that a block's last product may prepare for it
-            next_norm = self.blocks[order[i + 1].layer].first_norm() if i + 1 < len(order) else None
+            if i in self._injections:
+                pending = self._inject(self._injections[i], resid, pending, ctx)
+            # the norm that meets the stream next, so that a block's last product may prepare for it; none where
+            # the stream takes something up in between: the contribution then comes back as it is
+            follows = i + 1 < len(order) and (i + 1) not in self._injections
+            next_norm = self.blocks[order[i + 1].layer].first_norm() if follows else None
             pending = self.blocks[run.layer].forward(resid, pending, ctx, caches[i], next_norm=next_norm)
+            if self.layer_probe is not None:
+                delta, alpha = (None, 1.0) if isinstance(pending, ops.NormedInput) else ops.split_pending(pending)
+                self.layer_probe(i, resid if delta is None else resid + alpha * delta.to(resid.dtype))
         if ctx.num_logits == 0:
             return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=self.device)
-        x = self.final_norm.add_forward(resid, pending, rows=ctx.logit_rows)
+        delta, alpha = ops.split_pending(pending)
+        if alpha != 1.0:
+            x = self.final_norm.add_forward(resid, delta, rows=ctx.logit_rows, alpha=alpha)
+        else:
+            x = self.final_norm.add_forward(resid, delta, rows=ctx.logit_rows)
         return self.project_logits(x)
+
+    def _inject(self, inj, resid, pending, ctx):
+        """The stream takes up what the entry in front left, then the token embeddings and/or a vector of the plan."""
+        delta, alpha = ops.split_pending(pending)
+        vector = self._vectors[inj.vector][inj.row] if inj.vector is not None else None
+        if inj.add_embedding:
+            ops.stream_inject(resid, delta, alpha, ctx.token_ids, self.embedding, vector)
+        else:
+            ops.stream_inject(resid, delta, alpha, None, None, vector)
+        return None
 
     def _check_step(self, ctx, caches) -> None:
         """Checked mode: the step's arrays are looked over on the device before any kernel indexes with them."""
         slots = next((c.states.shape[0] for c in caches if hasattr(c, "states")), 0)
-        ops.check_step_arrays(ctx, self.plan.vocab_size, self.plan.max_positions, slots)
+        ops.check_step_arrays(ctx, self.plan.vocab_size, self.plan.max_positions or 0x7FFFFFFF, slots)
         seen = []
         for c in caches:
             if hasattr(c, "page_table") and all(c.page_table.data_ptr() != t.data_ptr() for t in seen):
@@ -144,4 +176,7 @@ class Model:
     def project_logits(self, x) -> torch.Tensor:
         """32-bit logits ``[rows, vocab]`` of the normalised rows ``x`` (a tensor, or the factored form that the
         last block handed on).  The place for an architecture's cap or scale of its logits, in a subclass."""
-        return ops.linear(x, self.head, out_dtype=torch.float32)
+        logits = ops.linear(x, self.head, out_dtype=torch.float32)
+        if self.plan.logit_scale != 1.0:
+            ops.unary(logits, "scale", self.plan.logit_scale, inplace=True)
+        return logits

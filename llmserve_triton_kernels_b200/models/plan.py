@@ -59,16 +59,31 @@ class LayerRun:
 
 
 @dataclass(frozen=True)
+class Injection:
+    """What the residual stream takes up before an entry of the order runs (after what the entry in front left has
+    been added): the token embeddings once more, and/or row ``row`` of the tensor ``vector`` ``[rows, hidden]``.
+    A stretch of layers that runs several times with the same weights marks its passes this way."""
+
+    before: int  # index into ``ModelPlan.schedule``
+    add_embedding: bool = False
+    vector: str | None = None  # name of a tensor declared in ``ModelPlan.extra_tensors``
+    row: int = 0
+
+
+@dataclass(frozen=True)
 class ModelPlan:
     hidden_size: int
     vocab_size: int
-    max_positions: int
+    max_positions: int | None  # None: no limit of the model's own (the cache's room bounds a request)
     embedding: str  # tensor name of the token table [vocab, hidden]
     layers: tuple[LayerSpec, ...]
     schedule: tuple[LayerRun, ...]
     final_norm: PartSpec
     head: str | None  # tensor name of the output matrix [vocab, hidden]; None: the token table
     ignored: tuple[str, ...] = ()  # names a checkpoint may carry that the model does not read (e.g. a copy of a tied head)
+    injections: tuple[Injection, ...] = ()
+    extra_tensors: tuple[tuple[str, tuple[int, ...]], ...] = ()  # (name, shape) of tensors that belong to no part
+    logit_scale: float = 1.0  # the logits are the output matrix's product times this
 
     def __post_init__(self) -> None:
         for i, run in enumerate(self.schedule):
@@ -79,3 +94,11 @@ class ModelPlan:
                     raise ValueError(f"schedule entry {i} reads the cache of entry {run.cache_of}, which is not earlier")
                 if self.schedule[run.cache_of].cache_of is not None:
                     raise ValueError(f"schedule entry {i} reads the cache of entry {run.cache_of}, which keeps none itself")
+        declared = {name for name, _ in self.extra_tensors}
+        seen = set()
+        for inj in self.injections:
+            if not 0 <= inj.before < len(self.schedule) or inj.before in seen:
+                raise ValueError(f"an injection names entry {inj.before} of {len(self.schedule)}, or an entry twice")
+            seen.add(inj.before)
+            if inj.vector is not None and inj.vector not in declared:
+                raise ValueError(f"an injection reads the tensor {inj.vector!r}, which the plan does not declare")

@@ -20,7 +20,7 @@ _F32, _BF16 = 0, 1
 _lib = None
 _lock = threading.Lock()
 
-_vp, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+_vp, _i, _f, _ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
 _SIGNATURES = {
     "llm_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _vp],
     "llm_rmsnorm": [_vp, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _vp],
@@ -42,6 +42,16 @@ _SIGNATURES = {
     "llm_attention_mma_routed": [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
     "llm_attention_tcgen05": [_vp, _i, _vp, _i, _vp, ctypes.c_longlong, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp],
     "llm_argmax": [_vp, _i, _i, _vp, _vp, _vp],
+    "llm_group_rmsnorm": [_vp, _vp, _i, _f, _vp, _f, _i, _vp, _vp, _i, _i, _i, _vp],
+    "llm_stream_inject": [_vp, _vp, _i, _f, _vp, _vp, _i, _i, _vp, _i, _i, _vp],
+    "llm_unary": [_vp, _i, _vp, _i, _i, _i, _i, _i, _f, _vp],
+    "llm_gate_mul": [_vp, _ll, _ll, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
+    "llm_mingru_scan": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "llm_latent_prepare": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _vp],
+    "llm_unit_norm_kv_write": [_vp, _i, _i, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "llm_attention_rows": [_vp, _ll, _ll, _i, _vp, _ll, _ll, _i, _vp, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _i, _i,
+                           _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp],
+    "llm_gemm_simt_batched": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _vp],
     "llm_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
 }
 
@@ -304,6 +314,22 @@ class _Added:
 ADDED = _Added()
 
 
+class Scaled:
+    """A contribution that enters the residual stream times ``alpha`` (layers that scale what their parts add)."""
+
+    def __init__(self, tensor: torch.Tensor, alpha: float):
+        self.tensor, self.alpha = tensor, float(alpha)
+
+
+def split_pending(pending) -> tuple[torch.Tensor | None, float]:
+    """``(what is still to be added to the stream or None, its factor)`` of what a part or a block returned."""
+    if pending is None or pending is ADDED:
+        return None, 1.0
+    if isinstance(pending, Scaled):
+        return pending.tensor, pending.alpha
+    return pending, 1.0
+
+
 class ResidualSink:
     """Where a part's last matrix product may put its result: added to the 32-bit residual stream ``resid`` in place.
     For few rows the fused decode kernel does it and hands the stream on normalised for ``norm`` (an RMS norm's
@@ -312,8 +338,9 @@ class ResidualSink:
     accumulated and written in 32-bit), and :data:`ADDED` is returned: no contribution travels through memory to be
     added by the norm's kernel, which then only reads the stream.  Built by a block for bfloat16 steps."""
 
-    def __init__(self, resid: torch.Tensor, weight: torch.Tensor | None, eps: float, norm=None):
-        self.resid, self.weight, self.eps, self.norm = resid, weight, float(eps), norm
+    def __init__(self, resid: torch.Tensor, weight: torch.Tensor | None, eps: float, norm=None, alpha: float = 1.0):
+        """``alpha``: the product enters the stream times this (only the library's way takes a factor other than 1)."""
+        self.resid, self.weight, self.eps, self.norm, self.alpha = resid, weight, float(eps), norm, float(alpha)
 
     @staticmethod
     def usable(num_tokens: int, dtype: torch.dtype) -> bool:
@@ -326,7 +353,7 @@ class ResidualSink:
         n = w.shape[0]
         if not (x.dtype == torch.bfloat16 and x.stride(1) == 1 and w.is_contiguous() and self.resid.is_contiguous()):
             return None
-        if m <= _DECODE_LINEAR_MAX_ROWS and self.weight is not None:
+        if m <= _DECODE_LINEAR_MAX_ROWS and self.weight is not None and self.alpha == 1.0:
             parts = -(-n // 16)
             xw = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
             ss = torch.empty((parts, m), dtype=torch.float32, device=x.device)
@@ -341,7 +368,7 @@ class ResidualSink:
         if _GEMM_POLICY == "own" and m >= _TCGEN05_MIN_ROWS:
             return None  # the caller runs the own tcgen05 product and leaves the sum to the norm's kernel
         library()
-        torch.addmm(self.resid, x, w.t(), out_dtype=torch.float32, out=self.resid)
+        torch.addmm(self.resid, x, w.t(), alpha=self.alpha, out_dtype=torch.float32, out=self.resid)
         return ADDED
 
     def linear_tcgen05(self, x: torch.Tensor, w: torch.Tensor) -> "NormedInput | None":
@@ -351,7 +378,7 @@ class ResidualSink:
         1.1B model took 6.04 ms this way against 5.46 ms with the sum left to the norm's kernel, so no part calls it."""
         m, k = x.shape
         n = w.shape[0]
-        if not (x.dtype == torch.bfloat16 and x.stride(1) == 1 and w.is_contiguous() and m >= _TCGEN05_MIN_ROWS and self.weight is not None):
+        if not (x.dtype == torch.bfloat16 and x.stride(1) == 1 and w.is_contiguous() and m >= _TCGEN05_MIN_ROWS and self.weight is not None and self.alpha == 1.0):
             return None
         parts = library().llm_gemm_tcgen05_parts(n)
         xw = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
@@ -760,3 +787,223 @@ def sample(
     )
     _check(code, "sample")
     return out
+
+
+# ------------------------------------------------------------------------------------------------
+# Operations of layers that normalise in groups, scale their contributions, gate their outputs, keep a recurrent
+# state, or attend over a latent (csrc/stream_ops.cu, recurrent.cu, cache_write.cu, attention_generic.cu).
+_UNARY_KINDS = {"relu2": 0, "gelu_tanh": 1, "scale": 2, "silu": 3}
+_GATE_KINDS = {"sigmoid": 0, "silu": 1}
+
+
+def group_rmsnorm(
+    resid: torch.Tensor,
+    weight: torch.Tensor,
+    eps: float,
+    groups: int,
+    delta: torch.Tensor | None = None,
+    alpha: float = 1.0,
+    rows: torch.Tensor | None = None,
+    out_dtype: torch.dtype = torch.float32,
+) -> torch.Tensor:
+    """``v = resid + alpha * delta``; each of ``groups`` equal consecutive parts of a row of ``v`` is divided by
+    ``sqrt(mean(part^2) + eps)``; returns that times ``weight`` in ``out_dtype``.  Without ``rows`` the sum is written
+    back to ``resid``; with ``rows`` (int32) only those rows are produced and ``resid`` is not changed."""
+    _need(resid.dtype == torch.float32 and resid.dim() == 2 and resid.is_contiguous(), "the residual must be a contiguous float32 matrix")
+    _need(weight.dtype == torch.float32 and weight.numel() == resid.shape[1], "the norm weight must be float32 of the row size")
+    _need(groups >= 1 and resid.shape[1] % groups == 0, f"rows of {resid.shape[1]} do not split into {groups} equal parts")
+    if delta is not None:
+        _need(delta.shape == resid.shape and delta.is_contiguous(), "delta must have the residual's shape")
+    if rows is not None:
+        _i32(rows, "rows")
+    n_out = resid.shape[0] if rows is None else rows.numel()
+    out = torch.empty((n_out, resid.shape[1]), dtype=out_dtype, device=resid.device)
+    code = _launch(
+        "llm_group_rmsnorm", _ptr(resid), _ptr(delta), _code(delta.dtype) if delta is not None else -1, float(alpha),
+        _ptr(weight), float(eps), int(groups), _ptr(rows), _ptr(out), _code(out_dtype), n_out, resid.shape[1], _stream(),
+    )
+    _check(code, "group_rmsnorm")
+    return out
+
+
+def stream_inject(
+    resid: torch.Tensor,
+    delta: torch.Tensor | None = None,
+    alpha: float = 1.0,
+    ids: torch.Tensor | None = None,
+    table: torch.Tensor | None = None,
+    vector: torch.Tensor | None = None,
+) -> None:
+    """``resid[t] += alpha * delta[t] + float(table[ids[t]]) + vector`` in place, in that order, each addend optional:
+    what a residual stream meets when a stretch of layers starts again."""
+    _need(resid.dtype == torch.float32 and resid.dim() == 2 and resid.is_contiguous(), "the residual must be a contiguous float32 matrix")
+    n, hidden = resid.shape
+    if delta is not None:
+        _need(delta.shape == resid.shape and delta.is_contiguous(), "delta must have the residual's shape")
+    if table is not None:
+        _i32(ids, "ids")
+        _need(table.dim() == 2 and table.is_contiguous() and table.shape[1] == hidden and ids.numel() == n, "the token table does not match the stream")
+    if vector is not None:
+        _need(vector.dtype == torch.float32 and vector.is_contiguous() and vector.numel() == hidden, "the vector must be float32 of the row size")
+    code = _launch(
+        "llm_stream_inject", _ptr(resid), _ptr(delta), _code(delta.dtype) if delta is not None else -1, float(alpha),
+        _ptr(ids) if table is not None else None, _ptr(table), _code(table.dtype) if table is not None else -1,
+        table.shape[0] if table is not None else 0, _ptr(vector), n, hidden, _stream(),
+    )
+    _check(code, "stream_inject")
+
+
+def unary(x: torch.Tensor, kind: str, alpha: float = 1.0, inplace: bool = False) -> torch.Tensor:
+    """A one-input function of every element, computed in 32-bit: ``relu2`` (the square of relu), ``gelu_tanh``,
+    ``silu``, or ``scale`` (``alpha * x``).  ``x [N, C]`` may have a row pitch."""
+    _need(kind in _UNARY_KINDS, f"no one-input function {kind!r}; known: {sorted(_UNARY_KINDS)}")
+    _need(x.dim() == 2 and x.stride(1) == 1, "unary: a matrix with unit inner stride")
+    out = x if inplace else torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    code = _launch("llm_unary", _ptr(x), x.stride(0), _ptr(out), out.stride(0), _code(x.dtype), x.shape[0], x.shape[1],
+                   _UNARY_KINDS[kind], float(alpha), _stream())
+    _check(code, "unary")
+    return out
+
+
+def linear_act(x, w: torch.Tensor, activation: str) -> torch.Tensor:
+    """``act(x @ w^T)`` for a one-input activation (see :func:`unary`): the product, then the activation on its
+    result in place."""
+    return unary(linear(x, w), activation, inplace=True)
+
+
+def gate_mul(a: torch.Tensor, b: torch.Tensor, kind: str = "sigmoid") -> torch.Tensor:
+    """``a [N, heads, W]`` (any token and head strides) times ``gate(b [N, heads * W])`` -> ``[N, heads * W]``;
+    the gate (``sigmoid`` or ``silu``) and the product are 32-bit."""
+    _need(kind in _GATE_KINDS, f"no gate {kind!r}; known: {sorted(_GATE_KINDS)}")
+    _need(a.dim() == 3 and a.stride(2) == 1 and b.dim() == 2 and b.stride(1) == 1 and a.dtype == b.dtype, "gate_mul: a [N, heads, W], b [N, heads * W]")
+    n, heads, w = a.shape
+    _need(b.shape[0] == n and b.shape[1] == heads * w, "gate_mul: the gate does not match the heads")
+    out = torch.empty((n, heads * w), dtype=a.dtype, device=a.device)
+    code = _launch("llm_gate_mul", _ptr(a), a.stride(0), a.stride(1), w, _ptr(b), b.stride(0), _ptr(out), heads * w,
+                   _code(a.dtype), n, heads * w, _GATE_KINDS[kind], _stream())
+    _check(code, "gate_mul")
+    return out
+
+
+def mingru_scan(proj: torch.Tensor, bias_z, bias_u, states: torch.Tensor, state_slots: torch.Tensor, cu_tokens: torch.Tensor,
+                num_requests: int, width: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """The minGRU recurrence over a flat batch.  ``proj [N, 3 * width]`` holds the pre-activations of the update
+    gate, the candidate and the output gate; ``states [slots, width]`` (float32) is read at ``state_slots[r]`` for
+    request r, walked over the request's tokens ``cu_tokens[r]:cu_tokens[r+1]`` and written back.  Returns
+    ``state_t * silu(output gate)`` ``[N, width]`` in ``out_dtype``."""
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] >= 3 * width, "mingru_scan: proj rows hold three pre-activations")
+    _need(states.dtype == torch.float32 and states.is_contiguous() and states.shape[1] == width, "mingru_scan: states must be float32 [slots, width]")
+    for b in (bias_z, bias_u):
+        _need(b is None or (b.dtype == torch.float32 and b.numel() == width and b.is_contiguous()), "mingru_scan: biases are float32 [width]")
+    _i32(state_slots, "state_slots")
+    _i32(cu_tokens, "cu_tokens")
+    out = torch.empty((proj.shape[0], width), dtype=out_dtype, device=proj.device)
+    code = _launch("llm_mingru_scan", _ptr(proj), _code(proj.dtype), proj.stride(0), _ptr(bias_z), _ptr(bias_u), _ptr(states),
+                   _ptr(state_slots), _ptr(cu_tokens), _ptr(out), _code(out_dtype), width, int(num_requests), width, _stream())
+    _check(code, "mingru_scan")
+    return out
+
+
+def latent_prepare(proj: torch.Tensor, positions: torch.Tensor, slot_map: torch.Tensor, plane: torch.Tensor, weight: torch.Tensor,
+                   freq: torch.Tensor, eps: float, heads: int, dim: int, rot: int, rank: int) -> torch.Tensor:
+    """For latent attention, from a token's stacked projections ``proj`` = ``[heads x (dim | rot) | rank | rot | ...]``:
+    the queries' rotated parts (interleaved pairs, angles ``position * freq[i]`` in 32-bit) are returned as
+    ``[N, heads, rot]``; the latent, RMS-normed with ``weight``, and the rotated shared key part are written to the
+    token's slot of ``plane [pages, page_size, rank + rot]``."""
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] >= heads * (dim + rot) + rank + rot, "latent_prepare: proj rows are too short")
+    _need(plane.dtype == proj.dtype and plane.is_contiguous() and plane.dim() == 3 and plane.shape[2] == rank + rot, "latent_prepare: the plane must be [pages, page_size, rank + rot] of the rows' type")
+    _need(weight.dtype == torch.float32 and weight.numel() == rank and freq.dtype == torch.float32 and freq.is_contiguous(), "latent_prepare: weight [rank] and freq are float32")
+    _i32(positions, "positions")
+    _i32(slot_map, "slot_map")
+    rot_dims = 2 * freq.numel()
+    q_rot = torch.empty((proj.shape[0], heads, rot), dtype=proj.dtype, device=proj.device)
+    code = _launch("llm_latent_prepare", _ptr(proj), _code(proj.dtype), proj.stride(0), _ptr(q_rot), _ptr(positions), _ptr(slot_map),
+                   _ptr(plane), _ptr(weight), _ptr(freq), float(eps), proj.shape[0], heads, dim, rot, rank, rot_dims, _stream())
+    _check(code, "latent_prepare")
+    return q_rot
+
+
+def unit_norm_kv_write(qkv: torch.Tensor, slot_map: torch.Tensor, pool: torch.Tensor, eps: float | None, heads: int, kv_heads: int,
+                       key_dim: int, value_dim: int) -> None:
+    """``qkv`` rows = ``[heads x key_dim | kv_heads x key_dim | kv_heads x value_dim]``.  With ``eps`` every query
+    head (in place) and key head is divided by its root mean square ``sqrt(mean(x^2) + eps)``; keys and values are
+    written to the row's slot of ``pool [pages, 2, kv_heads, page_size, D]`` (``D >= key_dim, value_dim``)."""
+    _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= (heads + kv_heads) * key_dim + kv_heads * value_dim, "unit_norm_kv_write: qkv rows are too short")
+    _need(pool.dtype == qkv.dtype and pool.is_contiguous() and pool.dim() == 5 and tuple(pool.shape[1:3]) == (2, kv_heads), "the pool plane does not match the heads")
+    _need(pool.shape[4] >= max(key_dim, value_dim), "the pool's rows are shorter than a key or a value")
+    _i32(slot_map, "slot_map")
+    code = _launch("llm_unit_norm_kv_write", _ptr(qkv), _code(qkv.dtype), qkv.stride(0), _ptr(slot_map), _ptr(pool),
+                   float(eps or 0.0), int(eps is not None), qkv.shape[0], heads, kv_heads, key_dim, value_dim, pool.shape[4],
+                   pool.shape[3], _stream())
+    _check(code, "unit_norm_kv_write")
+
+
+def head_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """One product per head: ``x [N, heads, K]`` (any token and head strides) times ``w [heads, M, K]`` ->
+    ``[N, heads, M]`` (a view whose strides the callers do not rely on).  float32 on the CUDA cores in true 32-bit;
+    bfloat16 through the vendor's batched product, 32-bit accumulation."""
+    _need(x.dim() == 3 and w.dim() == 3 and x.shape[1] == w.shape[0] and x.shape[2] == w.shape[2], f"head_linear: shapes {tuple(x.shape)} and {tuple(w.shape)} do not match")
+    _need(x.dtype == w.dtype and x.stride(2) == 1 and w.is_contiguous(), "head_linear: operands of one type, unit inner strides")
+    n, heads, k = x.shape
+    m = w.shape[1]
+    if x.dtype == torch.float32:
+        out = torch.empty((n, heads, m), dtype=x.dtype, device=x.device)
+        code = _launch("llm_gemm_simt_batched", _ptr(x), _ptr(w), _ptr(out), _F32, _F32, n, m, k, x.stride(0), k, heads * m,
+                       heads, x.stride(1), m * k, m, _stream())
+        _check(code, "head_linear (float32)")
+        return out
+    library()
+    return torch.bmm(x.transpose(0, 1), w.transpose(1, 2)).transpose(0, 1)
+
+
+def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, page_table, page_size: int, ctx, *, num_heads: int,
+                   num_kv_heads: int, scale: float, window: int | None = None, slopes: torch.Tensor | None = None) -> torch.Tensor:
+    """Attention in its general form: queries ``q0 [N, H, d0]`` and optionally ``q1 [N, H, d1]`` (lanes behind q0's),
+    keys and values addressed by ``(page, head, token)`` strides in elements, an optional bias ``-slopes[h] * distance``.
+    Returns ``[N, H, value_dim]``."""
+    n, d0 = q0.shape[0], q0.shape[2]
+    d1 = 0 if q1 is None else q1.shape[2]
+    _need(q0.stride(2) == 1 and (q1 is None or q1.stride(2) == 1), "attention_rows: queries need unit inner strides")
+    _i32(page_table, "page_table")
+    if slopes is not None:
+        _need(slopes.dtype == torch.float32 and slopes.numel() == num_heads and slopes.is_contiguous(), "slopes must be float32 [heads]")
+    out = torch.empty((n, num_heads, value_dim), dtype=q0.dtype, device=q0.device)
+    code = _launch(
+        "llm_attention_rows", _ptr(q0), q0.stride(0), q0.stride(1), d0, _ptr(q1), 0 if q1 is None else q1.stride(0),
+        0 if q1 is None else q1.stride(1), d1, _ptr(out), out.stride(0), out.stride(1), keys, *k_strides, values, *v_strides,
+        value_dim, _code(q0.dtype), _ptr(page_table), page_table.shape[1], _ptr(ctx.token_request), _ptr(ctx.cu_tokens),
+        _ptr(ctx.context_lens), _ptr(slopes), n, num_heads, num_kv_heads, page_size, int(window or 0), float(scale), _stream(),
+    )
+    _check(code, "attention_rows")
+    return out
+
+
+def latent_paged_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, plane: torch.Tensor, page_table: torch.Tensor, ctx, *,
+                           rank: int, scale: float, window: int | None = None) -> torch.Tensor:
+    """Attention of every new token over its request's cached latents.  A cached row ``[rank | rot]`` is the key of
+    every head (against the query ``[q_lat | q_rot]``) and, in its first ``rank`` lanes, the value.
+    ``plane [pages, page_size, rank + rot]``; returns ``[N, H, rank]``."""
+    _need(plane.dtype == q_lat.dtype and plane.is_contiguous() and plane.dim() == 3, "the plane must be contiguous [pages, page_size, width] of the query type")
+    page_size, width = plane.shape[1], plane.shape[2]
+    _need(q_lat.shape[2] == rank and q_lat.shape[2] + q_rot.shape[2] == width, "the queries do not match the cached rows")
+    strides = (page_size * width, 0, width)
+    return attention_rows(q_lat, q_rot, _ptr(plane), strides, _ptr(plane), strides, rank, page_table, page_size, ctx,
+                          num_heads=q_lat.shape[1], num_kv_heads=1, scale=scale, window=window)
+
+
+def biased_paged_attention(qkv: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor, ctx, *, num_heads: int, num_kv_heads: int,
+                           key_dim: int, value_dim: int, scale: float, window: int | None = None,
+                           slopes: torch.Tensor | None = None) -> torch.Tensor:
+    """Grouped-query attention whose keys and values may differ in size and whose scores may lose
+    ``slopes[h] * distance``.  ``qkv`` rows start with the query heads (``key_dim`` each); keys and values are in
+    ``pool [pages, 2, kv_heads, page_size, D]``.  Returns ``[N, num_heads * value_dim]``."""
+    _need(qkv.stride(1) == 1 and qkv.shape[1] >= num_heads * key_dim, "qkv rows must start with the query heads")
+    _need(pool.dtype == qkv.dtype and pool.is_contiguous() and pool.dim() == 5 and tuple(pool.shape[1:3]) == (2, num_kv_heads), "the pool plane does not match the heads")
+    page_size, row = pool.shape[3], pool.shape[4]
+    _need(row >= max(key_dim, value_dim), "the pool's rows are shorter than a key or a value")
+    q = qkv.as_strided((qkv.shape[0], num_heads, key_dim), (qkv.stride(0), key_dim, 1), qkv.storage_offset())
+    head, page = page_size * row, 2 * num_kv_heads * page_size * row
+    values = pool.data_ptr() + num_kv_heads * head * pool.element_size()
+    out = attention_rows(q, None, _ptr(pool), (page, head, row), values, (page, head, row), value_dim, page_table, page_size, ctx,
+                         num_heads=num_heads, num_kv_heads=num_kv_heads, scale=scale, window=window, slopes=slopes)
+    return out.view(qkv.shape[0], num_heads * value_dim)

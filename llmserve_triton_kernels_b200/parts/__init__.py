@@ -6,6 +6,7 @@ from .base import (  # noqa: F401
     Mixer,
     Norm,
     PagedKVSpec,
+    PagedRowSpec,
     Part,
     PartSpec,
     PositionEncoding,
@@ -14,4 +15,4 @@ from .base import (  # noqa: F401
     build_part,
     register_part,
 )
-from . import attention, block, feed_forward, norm, rotary  # noqa: F401,E402
+from . import attention, block, feed_forward, latent_attention, norm, recurrent, rotary  # noqa: F401,E402

@@ -11,6 +11,12 @@ projections and reads the cache that an earlier layer of the order wrote.  ``qkv
 src/llmserve/model/llama.py:64-66) give the projections bias vectors ``*_proj.bias``: such a layer
 runs its products and the bias sums as kernels of their own, not the fused decode kernels.
 
+Three options lead off the fused kernels onto the general ones (``ops.unit_norm_kv_write`` and
+``ops.biased_paged_attention``): ``value_dim`` (values of another size than queries and keys), ``qk_norm_eps`` (every
+query and key head is divided by its root mean square ``sqrt(mean(x^2) + eps)``, a norm without a weight), and
+``distance_bias`` b (the score of key j for the query at position i loses ``slope_h * (i - j)`` with
+``slope_h = 2^(-b (h+1) / num_heads)``).  ``tensor_names`` renames the four matrices.
+
 The position encoding is a part of its own.  One whose ``rotary_layout`` is ``"half"`` (pairs
 ``(j, j + head_dim/2)`` over the whole head, angles tabulated as ``rotary_table``) is applied by the
 kernels that also store keys and values; any other is asked to ``apply`` itself to q and k.
@@ -37,6 +43,10 @@ class PagedAttention(Mixer):
         own_kv: bool = True,
         qkv_bias: bool = False,
         out_bias: bool = False,
+        value_dim: int | None = None,
+        qk_norm_eps: float | None = None,
+        distance_bias: float | None = None,
+        tensor_names: dict[str, str] | None = None,
     ):
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads {num_heads} is not a multiple of num_kv_heads {num_kv_heads}")
@@ -53,6 +63,16 @@ class PagedAttention(Mixer):
         self.own_kv = bool(own_kv)
         self.qkv_bias = bool(qkv_bias)
         self.out_bias = bool(out_bias)
+        self.value_dim = self.head_dim if value_dim is None else int(value_dim)
+        if not 1 <= self.value_dim <= 256:
+            raise ValueError(f"value_dim {value_dim} is not supported: the attention kernels take value sizes up to 256")
+        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
+        self.distance_bias = None if distance_bias is None else float(distance_bias)
+        self.general = self.value_dim != self.head_dim or self.qk_norm_eps is not None or self.distance_bias is not None
+        if self.general and (position is not None or not own_kv or qkv_bias or out_bias):
+            raise ValueError("value_dim, qk_norm_eps and distance_bias are built for layers with keys and values of their own, no position part and no biases")
+        self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight", **(tensor_names or {})}
+        self.slopes: torch.Tensor | None = None  # [H] float32 with distance_bias
         self.b_in: torch.Tensor | None = None  # [(H + 2 KV) D] with qkv_bias
         self.b_out: torch.Tensor | None = None  # [hidden] with out_bias
         self.position = build_part("position", position) if position is not None else None
@@ -62,34 +82,38 @@ class PagedAttention(Mixer):
     def tensors(self) -> dict[str, TensorSpec]:
         q = self.num_heads * self.head_dim
         kv = self.num_kv_heads * self.head_dim
-        specs = {"q_proj.weight": TensorSpec((q, self.hidden_size))}
+        n = self.names
+        specs = {n["q"]: TensorSpec((q, self.hidden_size))}
         if self.own_kv:
-            specs["k_proj.weight"] = TensorSpec((kv, self.hidden_size))
-            specs["v_proj.weight"] = TensorSpec((kv, self.hidden_size))
-        specs["o_proj.weight"] = TensorSpec((self.hidden_size, q))
+            specs[n["k"]] = TensorSpec((kv, self.hidden_size))
+            specs[n["v"]] = TensorSpec((self.num_kv_heads * self.value_dim, self.hidden_size))
+        specs[n["o"]] = TensorSpec((self.hidden_size, self.num_heads * self.value_dim))
         if self.qkv_bias:
-            specs["q_proj.bias"] = TensorSpec((q,))
+            specs[n["q"].replace(".weight", ".bias")] = TensorSpec((q,))
             if self.own_kv:
-                specs["k_proj.bias"] = TensorSpec((kv,))
-                specs["v_proj.bias"] = TensorSpec((kv,))
+                specs[n["k"].replace(".weight", ".bias")] = TensorSpec((kv,))
+                specs[n["v"].replace(".weight", ".bias")] = TensorSpec((kv,))
         if self.out_bias:
-            specs["o_proj.bias"] = TensorSpec((self.hidden_size,))
+            specs[n["o"].replace(".weight", ".bias")] = TensorSpec((self.hidden_size,))
         return specs
 
     def bind(self, tensors, dtype, device) -> None:
-        names = ["q_proj.weight"] + (["k_proj.weight", "v_proj.weight"] if self.own_kv else [])
+        names = [self.names["q"]] + ([self.names["k"], self.names["v"]] if self.own_kv else [])
         fused = torch.cat([tensors[n].to(dtype) for n in names], dim=0)
         self.w_in = fused.to(device).contiguous()
-        self.w_out = tensors["o_proj.weight"].to(device=device, dtype=dtype).contiguous()
+        self.w_out = tensors[self.names["o"]].to(device=device, dtype=dtype).contiguous()
+        if self.distance_bias is not None:
+            heads = torch.arange(1, self.num_heads + 1, dtype=torch.float64)
+            self.slopes = torch.pow(2.0, -self.distance_bias * heads / self.num_heads).to(torch.float32).to(device)
         if self.qkv_bias:
             self.b_in = torch.cat([tensors[n.replace(".weight", ".bias")].to(dtype) for n in names]).to(device).contiguous()
         if self.out_bias:
-            self.b_out = tensors["o_proj.bias"].to(device=device, dtype=dtype).contiguous()
+            self.b_out = tensors[self.names["o"].replace(".weight", ".bias")].to(device=device, dtype=dtype).contiguous()
         if self.position is not None:
             self.position.bind({}, dtype, device)
 
     def cache_spec(self) -> PagedKVSpec:
-        return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window)
+        return PagedKVSpec(self.num_kv_heads, max(self.head_dim, self.value_dim), self.window)
 
     accepts_sink = True
 
@@ -107,6 +131,8 @@ class PagedAttention(Mixer):
 
     def forward(self, x, ctx, cache, sink=None):
         H, KV, D = self.num_heads, self.num_kv_heads, self.head_dim
+        if self.general:
+            return self._forward_general(x, ctx, cache, sink)
         table = self._rotary_table()
         qkv = None
         if (self.position is None or table is not None) and self.b_in is None:
@@ -130,6 +156,21 @@ class PagedAttention(Mixer):
         # the contribution to the 32-bit residual stream leaves the product in 32-bit: it is the sum's largest addend
         if self.b_out is not None:
             return ops.add_bias(ops.linear(out, self.w_out, out_dtype=torch.float32), self.b_out.float())
+        if sink is not None:
+            handed_on = sink.linear(out, self.w_out)
+            if handed_on is not None:
+                return handed_on
+        return ops.linear(out, self.w_out, out_dtype=torch.float32)
+
+    def _forward_general(self, x, ctx, cache, sink):
+        """Projection, the unit-RMS norms with the cache write, attention with its bias, output projection."""
+        H, KV = self.num_heads, self.num_kv_heads
+        qkv = ops.linear(x, self.w_in)
+        ops.unit_norm_kv_write(qkv, cache.slot_map, cache.pool, self.qk_norm_eps, H, KV, self.head_dim, self.value_dim)
+        out = ops.biased_paged_attention(
+            qkv, cache.pool, cache.page_table, ctx, num_heads=H, num_kv_heads=KV, key_dim=self.head_dim,
+            value_dim=self.value_dim, scale=self.scale, window=self.window, slopes=self.slopes,
+        )
         if sink is not None:
             handed_on = sink.linear(out, self.w_out)
             if handed_on is not None:

@@ -58,6 +58,15 @@ class PagedKVSpec:
 
 
 @dataclass(frozen=True)
+class PagedRowSpec:
+    """A mixer that keeps one row of ``width`` elements for every token (``window`` None) or for the last
+    ``window`` tokens only: a latent that is key and value of every head at once, for instance."""
+
+    width: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
 class StateSpec:
     """A mixer that keeps one tensor of fixed shape per request, zeroed when the request starts."""
 
@@ -88,15 +97,15 @@ class Norm(Part):
         raise NotImplementedError
 
     def add_forward(
-        self, resid: torch.Tensor, delta: torch.Tensor | None, rows: torch.Tensor | None = None
+        self, resid: torch.Tensor, delta: torch.Tensor | None, rows: torch.Tensor | None = None, alpha: float = 1.0
     ) -> torch.Tensor:
-        """``resid += delta`` in 32-bit, then normalise.  With ``rows`` only those rows are
+        """``resid += alpha * delta`` in 32-bit, then normalise.  With ``rows`` only those rows are
         produced and ``resid`` is left as it was.  A norm may fuse the two; this default does not."""
         if delta is not None:
             if rows is None:
-                resid.add_(delta.to(resid.dtype))
+                resid.add_(delta.to(resid.dtype), alpha=alpha)
             else:
-                return self.forward(resid[rows.long()] + delta[rows.long()].to(resid.dtype))
+                return self.forward(resid[rows.long()] + alpha * delta[rows.long()].to(resid.dtype))
         return self.forward(resid, rows)
 
 
@@ -115,7 +124,7 @@ class PositionEncoding(Part):
 class Mixer(Part):
     category = "mixer"
 
-    def cache_spec(self) -> PagedKVSpec | StateSpec | None:
+    def cache_spec(self) -> PagedKVSpec | PagedRowSpec | StateSpec | None:
         return None
 
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
@@ -141,6 +150,8 @@ class Block(Part):
 
     category = "block"
     roles: dict[str, str] = {}
+    # every contribution of this block's parts enters the residual stream times this
+    residual_scale: float = 1.0
 
     def owned_parts(self) -> list[Part]:
         """The parts of this block, in the order of ``roles``."""

@@ -10,6 +10,8 @@ no norm launches of its own; a large step's product leaves a norm kernel that on
 
 from __future__ import annotations
 
+import torch
+
 from .. import ops
 from .base import Block, FeedForward, Mixer, Norm, register_part
 
@@ -17,11 +19,12 @@ from .base import Block, FeedForward, Mixer, Norm, register_part
 class PreNormBlock(Block):
     roles = {"mixer_norm": "norm", "mixer": "mixer", "ff_norm": "norm", "feed_forward": "feed_forward"}
 
-    def __init__(self, mixer_norm: Norm, mixer: Mixer, ff_norm: Norm, feed_forward: FeedForward):
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, ff_norm: Norm, feed_forward: FeedForward, residual_scale: float = 1.0):
         self.mixer_norm = mixer_norm
         self.mixer = mixer
         self.ff_norm = ff_norm
         self.feed_forward = feed_forward
+        self.residual_scale = float(residual_scale)  # x += residual_scale * part(norm(x))
 
     @property
     def graph_safe(self) -> bool:
@@ -31,25 +34,31 @@ class PreNormBlock(Block):
         x = self._normed(self.mixer_norm, resid, pending, self.mixer)
         sink = self._sink(self.mixer, self.ff_norm, resid, ctx)
         pending = self.mixer.forward(x, ctx, cache, sink=sink) if sink else self.mixer.forward(x, ctx, cache)
-        x = self._normed(self.ff_norm, resid, pending, self.feed_forward)
+        x = self._normed(self.ff_norm, resid, self._scaled(pending), self.feed_forward)
         sink = self._sink(self.feed_forward, next_norm, resid, ctx)
-        return self.feed_forward.forward(x, ctx, sink=sink) if sink else self.feed_forward.forward(x, ctx)
+        return self._scaled(self.feed_forward.forward(x, ctx, sink=sink) if sink else self.feed_forward.forward(x, ctx))
+
+    def _scaled(self, pending):
+        """A part's contribution as the stream is to take it: times this block's ``residual_scale``."""
+        if self.residual_scale != 1.0 and isinstance(pending, torch.Tensor):
+            return ops.Scaled(pending, self.residual_scale)
+        return pending
 
     @staticmethod
     def _normed(norm, resid, pending, consumer):
-        """``pending`` is a contribution still to be added, or the stream already summed and
-        normalised for ``norm`` by the part before (a fused decode kernel did both).  A consumer
+        """``pending`` is a contribution still to be added (a tensor, or one with its factor), or the stream already
+        summed and normalised for ``norm`` by the part before (a fused decode kernel did both).  A consumer
         that does not say it takes the factored form gets a plain tensor."""
         if isinstance(pending, ops.NormedInput):
             if pending.norm is not norm:
                 raise RuntimeError("a part handed the residual stream on normalised for another norm")
             return pending if getattr(consumer, "accepts_sink", False) else pending.materialize()
-        if pending is ops.ADDED:  # the part's last product added its result to the stream itself
-            pending = None
-        return norm.add_forward(resid, pending)
+        delta, alpha = ops.split_pending(pending)
+        if alpha != 1.0:
+            return norm.add_forward(resid, delta, alpha=alpha)
+        return norm.add_forward(resid, delta)
 
-    @staticmethod
-    def _sink(part, norm, resid, ctx):
+    def _sink(self, part, norm, resid, ctx):
         """A sink for the part's last product, if the part takes one and another norm follows (the last part of the
         last layer keeps its contribution: only the rows whose logits are wanted are summed).  Where that norm is an
         RMS norm its weight goes along, so that a small step's product can hand the stream on normalised."""
@@ -59,7 +68,30 @@ class PreNormBlock(Block):
             return None
         fused = getattr(norm, "fused_params", None)
         weight, eps = fused() if fused is not None else (None, 0.0)
-        return ops.ResidualSink(resid, weight, eps, norm)
+        if self.residual_scale != 1.0:
+            weight = None  # the product that also normalises adds its result unscaled
+        return ops.ResidualSink(resid, weight, eps, norm, alpha=self.residual_scale)
+
+
+class MixerOnlyBlock(PreNormBlock):
+    """A layer without a feed-forward: ``x += residual_scale * mixer(norm(x))``."""
+
+    roles = {"mixer_norm": "norm", "mixer": "mixer"}
+
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, residual_scale: float = 1.0):
+        self.mixer_norm = mixer_norm
+        self.mixer = mixer
+        self.residual_scale = float(residual_scale)
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(p.graph_safe for p in (self.mixer_norm, self.mixer))
+
+    def forward(self, resid, pending, ctx, cache, next_norm=None):
+        x = self._normed(self.mixer_norm, resid, pending, self.mixer)
+        sink = self._sink(self.mixer, next_norm, resid, ctx)
+        return self._scaled(self.mixer.forward(x, ctx, cache, sink=sink) if sink else self.mixer.forward(x, ctx, cache))
 
 
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "pre_norm_mixer_only", MixerOnlyBlock)

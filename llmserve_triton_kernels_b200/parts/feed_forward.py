@@ -65,3 +65,39 @@ class GatedMLP(FeedForward):
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)
+
+
+class DenseMLP(FeedForward):
+    """``down(act(up(x)))`` without biases; ``act`` one of ``relu2`` (the square of relu), ``gelu_tanh``, ``silu``.
+    ``tensor_names``: local names of the two matrices (default ``up`` and ``down``)."""
+
+    graph_safe = True
+    accepts_sink = True
+    activations = ("relu2", "gelu_tanh", "silu")
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "relu2", tensor_names: dict[str, str] | None = None):
+        if activation not in self.activations:
+            raise ValueError(f"activation {activation!r} is not built; known: {self.activations}")
+        self.hidden_size, self.intermediate_size, self.activation = int(hidden_size), int(intermediate_size), activation
+        self.names = {"up": "up", "down": "down", **(tensor_names or {})}
+        self.w_up: torch.Tensor | None = None  # [I, hidden]
+        self.w_down: torch.Tensor | None = None  # [hidden, I]
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        i, h = self.intermediate_size, self.hidden_size
+        return {self.names["up"]: TensorSpec((i, h)), self.names["down"]: TensorSpec((h, i))}
+
+    def bind(self, tensors, dtype, device) -> None:
+        self.w_up = tensors[self.names["up"]].to(device=device, dtype=dtype).contiguous()
+        self.w_down = tensors[self.names["down"]].to(device=device, dtype=dtype).contiguous()
+
+    def forward(self, x, ctx, sink=None):
+        act = ops.linear_act(x, self.w_up, self.activation)
+        if sink is not None:
+            handed_on = sink.linear(act, self.w_down)
+            if handed_on is not None:
+                return handed_on
+        return ops.linear(act, self.w_down, out_dtype=torch.float32)
+
+
+register_part("feed_forward", "dense_mlp", DenseMLP)

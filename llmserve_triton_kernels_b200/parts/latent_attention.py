@@ -1,0 +1,112 @@
+"""Attention through a low-rank latent, over a paged cache of one row per token.
+
+A token's keys and values of all heads are products of one latent vector ``c`` (``rank`` lanes): the key of head h
+is ``[W_uk[h] c | k_rot]`` with a rotated part ``k_rot`` (``rot_dim`` lanes) that all heads share, its value is
+``W_uv[h] c``.  Only ``[c | k_rot]`` is cached.  The products with ``W_uk`` and ``W_uv`` are moved to the query side:
+
+    score(i, j, h) = (W_uk[h]^T q_plain[i, h]) . c[j] + q_rot[i, h] . k_rot[j]
+    out(i, h)      = W_uv[h] (sum_j weight(i, j, h) c[j])
+
+so that attention runs over the cached rows themselves: every head reads the same row as its key (all
+``rank + rot_dim`` lanes) and as its value (the first ``rank``).  The latent is RMS-normed (a weight of its own)
+before it is cached; rotary positions use the interleaved layout (lanes 2i and 2i+1 form a pair) with angles
+computed in 32-bit from the position; the concatenated heads are multiplied by ``sigmoid(W_g x)`` before the output
+projection.  Sizes, the softmax scale, the rotary base and the names of the tensors are parameters.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import Mixer, PagedRowSpec, TensorSpec, register_part
+
+_NAMES = {"q": "q", "down": "dkv", "latent_norm": "dkv.norm", "up_k": "uk", "up_v": "uv", "gate": "g", "out": "o"}
+
+
+class LatentAttention(Mixer):
+    graph_safe = True
+    accepts_sink = True
+
+    def __init__(
+        self,
+        hidden_size: int,
+        num_heads: int,
+        head_dim: int,
+        rot_dim: int,
+        value_dim: int,
+        rank: int,
+        scale: float,
+        rotary_base: float,
+        rotary_dims: int | None = None,
+        norm_eps: float = 1e-6,
+        output_gate: bool = True,
+        window: int | None = None,
+        tensor_names: dict[str, str] | None = None,
+    ):
+        self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
+        self.head_dim, self.rot_dim, self.value_dim, self.rank = int(head_dim), int(rot_dim), int(value_dim), int(rank)
+        self.scale, self.rotary_base, self.norm_eps = float(scale), float(rotary_base), float(norm_eps)
+        self.rotary_dims = self.rot_dim if rotary_dims is None else int(rotary_dims)
+        if self.rotary_dims % 2 or not 0 <= self.rotary_dims <= self.rot_dim:
+            raise ValueError(f"{rotary_dims} rotated lanes do not fit a rotated part of {rot_dim}")
+        if self.rank + self.rot_dim > 640 or self.rank > 512:
+            raise ValueError(f"a cached row of {rank} + {rot_dim} lanes is not supported: the attention kernels take rows up to 640 with a latent up to 512")
+        self.output_gate = bool(output_gate)
+        self.window = None if window is None else int(window)
+        self.names = {**_NAMES, **(tensor_names or {})}
+        self.w_in = self.w_uk_t = self.w_uv = self.w_out = self.latent_weight = self.freq = None
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        H, n = self.num_heads, self.names
+        specs = {
+            n["q"]: TensorSpec((H * (self.head_dim + self.rot_dim), self.hidden_size)),
+            n["down"]: TensorSpec((self.rank + self.rot_dim, self.hidden_size)),
+            n["latent_norm"]: TensorSpec((self.rank,), init="ones_plus_normal"),
+            n["up_k"]: TensorSpec((H * self.head_dim, self.rank)),
+            n["up_v"]: TensorSpec((H * self.value_dim, self.rank)),
+            n["out"]: TensorSpec((self.hidden_size, H * self.value_dim)),
+        }
+        if self.output_gate:
+            specs[n["gate"]] = TensorSpec((H * self.value_dim, self.hidden_size))
+        return specs
+
+    def bind(self, tensors, dtype, device) -> None:
+        H, n = self.num_heads, self.names
+        stacked = [tensors[n["q"]], tensors[n["down"]]] + ([tensors[n["gate"]]] if self.output_gate else [])
+        self.w_in = torch.cat([t.to(dtype) for t in stacked], dim=0).to(device).contiguous()
+        # W_uk per head, turned so that it multiplies the query: [H, rank, head_dim]
+        self.w_uk_t = tensors[n["up_k"]].to(dtype).view(H, self.head_dim, self.rank).transpose(1, 2).contiguous().to(device)
+        self.w_uv = tensors[n["up_v"]].to(dtype).view(H, self.value_dim, self.rank).contiguous().to(device)
+        self.w_out = tensors[n["out"]].to(device=device, dtype=dtype).contiguous()
+        self.latent_weight = tensors[n["latent_norm"]].to(device=device, dtype=torch.float32).contiguous()
+        pairs = torch.arange(self.rotary_dims // 2, dtype=torch.float64)
+        self.freq = (self.rotary_base ** (-2.0 * pairs / max(self.rotary_dims, 1))).to(torch.float32).to(device)
+
+    def cache_spec(self) -> PagedRowSpec:
+        return PagedRowSpec(self.rank + self.rot_dim, self.window)
+
+    def forward(self, x, ctx, cache, sink=None):
+        H, dim, rot, rank = self.num_heads, self.head_dim, self.rot_dim, self.rank
+        proj = ops.linear(x, self.w_in)  # [N, H (dim | rot) | rank | rot | H vdim]
+        q_rot = ops.latent_prepare(
+            proj, ctx.positions, cache.slot_map, cache.pool, self.latent_weight, self.freq, self.norm_eps, H, dim, rot, rank
+        )
+        q_plain = proj.as_strided((proj.shape[0], H, dim), (proj.stride(0), dim + rot, 1), proj.storage_offset())
+        q_lat = ops.head_linear(q_plain, self.w_uk_t)  # [N, H, rank]
+        mixed = ops.latent_paged_attention(
+            q_lat, q_rot, cache.pool, cache.page_table, ctx, rank=rank, scale=self.scale, window=self.window
+        )
+        heads = ops.head_linear(mixed, self.w_uv)  # [N, H, vdim]
+        if self.output_gate:
+            out = ops.gate_mul(heads, proj[:, H * (dim + rot) + rank + rot :], "sigmoid")
+        else:
+            out = heads.reshape(proj.shape[0], H * self.value_dim)
+        if sink is not None:
+            handed_on = sink.linear(out, self.w_out)
+            if handed_on is not None:
+                return handed_on
+        return ops.linear(out, self.w_out, out_dtype=torch.float32)
+
+
+register_part("mixer", "latent_attention", LatentAttention)

@@ -14,30 +14,42 @@ from .base import Norm, TensorSpec, register_part
 
 
 class RMSNorm(Norm):
+    """``groups`` > 1: the row is split into that many equal consecutive parts and each is divided by its own root
+    mean square (eps inside the root); the weight spans the whole row.  ``weight_name``: the local name of the
+    weight tensor (checkpoints that call a norm's weight by the norm's own name pass that name with an empty prefix
+    in front)."""
+
     graph_safe = True
 
-    def __init__(self, size: int, eps: float):
+    def __init__(self, size: int, eps: float, groups: int = 1, weight_name: str = "weight"):
         self.size = int(size)
         self.eps = float(eps)
+        self.groups = int(groups)
+        if self.groups < 1 or self.size % self.groups:
+            raise ValueError(f"a row of {self.size} does not split into {groups} equal parts")
+        self.weight_name = weight_name
         self.weight: torch.Tensor | None = None
         self.out_dtype: torch.dtype | None = None
 
     def tensors(self) -> dict[str, TensorSpec]:
-        return {"weight": TensorSpec((self.size,), init="ones_plus_normal")}
+        return {self.weight_name: TensorSpec((self.size,), init="ones_plus_normal")}
 
     def bind(self, tensors, dtype, device) -> None:
-        self.weight = tensors["weight"].to(device=device, dtype=torch.float32).contiguous()
+        self.weight = tensors[self.weight_name].to(device=device, dtype=torch.float32).contiguous()
         self.out_dtype = dtype
 
     def fused_params(self):
-        """``(weight, eps)``: what a product needs to fold this norm into its ends."""
-        return self.weight, self.eps
+        """``(weight, eps)``: what a product needs to fold this norm into its ends; a norm in groups cannot be
+        folded (its scale is not one number per row) and says ``(None, eps)``."""
+        return (self.weight if self.groups == 1 else None), self.eps
 
     def forward(self, x, rows=None):
-        return ops.rmsnorm(x, self.weight, self.eps, delta=None, rows=rows, out_dtype=self.out_dtype)
+        return self.add_forward(x, None, rows)
 
-    def add_forward(self, resid, delta, rows=None):
-        return ops.rmsnorm(resid, self.weight, self.eps, delta=delta, rows=rows, out_dtype=self.out_dtype)
+    def add_forward(self, resid, delta, rows=None, alpha: float = 1.0):
+        if self.groups == 1 and alpha == 1.0:
+            return ops.rmsnorm(resid, self.weight, self.eps, delta=delta, rows=rows, out_dtype=self.out_dtype)
+        return ops.group_rmsnorm(resid, self.weight, self.eps, self.groups, delta=delta, alpha=alpha, rows=rows, out_dtype=self.out_dtype)
 
 
 register_part("norm", "rms_norm", RMSNorm)

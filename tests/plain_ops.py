@@ -126,7 +126,180 @@ def sample(logits, temperature, top_k, top_p, seeds, counters):
     return torch.tensor(out, dtype=torch.int32, device=logits.device)
 
 
+# ---------------------------------------------------------------------------------------------
+# operations of layers that normalise in groups, scale their contributions, gate, recur or attend over a latent
+def group_rmsnorm(resid, weight, eps, groups, delta=None, alpha=1.0, rows=None, out_dtype=torch.float32):
+    if rows is not None:
+        v = resid[rows.long()]
+        if delta is not None:
+            v = v + alpha * delta[rows.long()].float()
+    else:
+        if delta is not None:
+            resid.add_(delta.float(), alpha=alpha)
+        v = resid
+    n, d = v.shape
+    parts = v.view(n, groups, d // groups)
+    y = (parts / torch.sqrt(parts.pow(2).mean(-1, keepdim=True) + eps)).reshape(n, d) * weight
+    return y.to(out_dtype)
+
+
+def stream_inject(resid, delta=None, alpha=1.0, ids=None, table=None, vector=None):
+    if delta is not None:
+        resid.add_(delta.float(), alpha=alpha)
+    if table is not None:
+        resid.add_(table[ids.long()].float())
+    if vector is not None:
+        resid.add_(vector)
+
+
+def unary(x, kind, alpha=1.0, inplace=False):
+    v = x.float()
+    if kind == "relu2":
+        y = torch.relu(v).pow(2)
+    elif kind == "gelu_tanh":
+        y = 0.5 * v * (1 + torch.tanh(0.7978845608028654 * (v + 0.044715 * v.pow(3))))
+    elif kind == "scale":
+        y = alpha * v
+    elif kind == "silu":
+        y = v * torch.sigmoid(v)
+    else:
+        raise ValueError(kind)
+    if inplace:
+        x.copy_(y.to(x.dtype))
+        return x
+    return y.to(x.dtype)
+
+
+def linear_act(x, w, activation):
+    return unary(linear(x, w), activation, inplace=True)
+
+
+def gate_mul(a, b, kind="sigmoid"):
+    n, heads, w = a.shape
+    g = b.float()
+    g = torch.sigmoid(g) if kind == "sigmoid" else g * torch.sigmoid(g)
+    return (a.float().reshape(n, heads * w) * g).to(a.dtype)
+
+
+def mingru_scan(proj, bias_z, bias_u, states, state_slots, cu_tokens, num_requests, width, out_dtype):
+    out = torch.empty((proj.shape[0], width), dtype=out_dtype, device=proj.device)
+    p = proj.float()
+    cu = cu_tokens.tolist()
+    for r in range(num_requests):
+        slot = int(state_slots[r])
+        s = states[slot].clone()
+        for t in range(cu[r], cu[r + 1]):
+            z = torch.sigmoid(p[t, :width] + (bias_z if bias_z is not None else 0))
+            u = p[t, width : 2 * width] + (bias_u if bias_u is not None else 0)
+            c = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+            s = (1 - z) * s + z * c
+            g = p[t, 2 * width : 3 * width]
+            out[t] = (s * g * torch.sigmoid(g)).to(out_dtype)
+        states[slot] = s
+    return out
+
+
+def _rotate_interleaved(x, positions, freq):
+    """x [N, ..., lanes] float32; the first 2 * len(freq) lanes turn in pairs (2i, 2i + 1)."""
+    dims = 2 * freq.numel()
+    angle = positions.float()[:, None] * freq
+    shape = [x.shape[0]] + [1] * (x.dim() - 2) + [dims // 2]
+    cos, sin = angle.cos().view(shape), angle.sin().view(shape)
+    out = x.clone()
+    u, v = x[..., 0:dims:2], x[..., 1:dims:2]
+    out[..., 0:dims:2] = u * cos - v * sin
+    out[..., 1:dims:2] = v * cos + u * sin
+    return out
+
+
+def latent_prepare(proj, positions, slot_map, plane, weight, freq, eps, heads, dim, rot, rank):
+    n = proj.shape[0]
+    q = proj[:, : heads * (dim + rot)].float().view(n, heads, dim + rot)
+    q_rot = _rotate_interleaved(q[..., dim:], positions, freq).to(proj.dtype)
+    base = heads * (dim + rot)
+    latent = proj[:, base : base + rank].float()
+    latent = latent / torch.sqrt(latent.pow(2).mean(-1, keepdim=True) + eps) * weight
+    k_rot = _rotate_interleaved(proj[:, base + rank : base + rank + rot].float(), positions, freq)
+    page_size = plane.shape[1]
+    page, off = (slot_map // page_size).long(), (slot_map % page_size).long()
+    plane[page, off] = torch.cat((latent, k_rot), dim=-1).to(plane.dtype)
+    return q_rot
+
+
+def unit_norm_kv_write(qkv, slot_map, pool, eps, heads, kv_heads, key_dim, value_dim):
+    n = qkv.shape[0]
+    qk = qkv[:, : (heads + kv_heads) * key_dim].float().view(n, heads + kv_heads, key_dim)
+    if eps is not None:
+        qk = qk / torch.sqrt(qk.pow(2).mean(-1, keepdim=True) + eps)
+    qkv[:, : heads * key_dim] = qk[:, :heads].reshape(n, -1).to(qkv.dtype)
+    v = qkv[:, (heads + kv_heads) * key_dim : (heads + kv_heads) * key_dim + kv_heads * value_dim].view(n, kv_heads, value_dim)
+    page_size = pool.shape[3]
+    page, off = (slot_map // page_size).long(), (slot_map % page_size).long()
+    pool[page, 0, :, off, :key_dim] = qk[:, heads:].to(pool.dtype)
+    pool[page, 1, :, off, :value_dim] = v.to(pool.dtype)
+
+
+def head_linear(x, w):
+    return torch.einsum("nhk,hmk->nhm", x.float(), w.float()).to(x.dtype)
+
+
+def _attend(q, k, v, first_pos, scale, window, slopes):
+    """q [T, H, dk], k [n, H, dk], v [n, H, dv] float32; query t stands at position first_pos + t."""
+    n = k.shape[0]
+    s = torch.einsum("thd,jhd->htj", q, k) * scale
+    pos = torch.arange(first_pos, first_pos + q.shape[0])[:, None]
+    j = torch.arange(n)[None, :]
+    if slopes is not None:
+        s = s - slopes.float()[:, None, None] * (pos - j).float()
+    visible = j <= pos
+    if window:
+        visible = visible & (j > pos - window)
+    s = s.masked_fill(~visible[None], float("-inf"))
+    return torch.einsum("htj,jhd->thd", torch.softmax(s, dim=-1), v)
+
+
+def latent_paged_attention(q_lat, q_rot, plane, page_table, ctx, *, rank, scale, window=None):
+    page_size = plane.shape[1]
+    n_tok, heads = q_lat.shape[0], q_lat.shape[1]
+    out = torch.empty((n_tok, heads, rank), dtype=q_lat.dtype, device=q_lat.device)
+    cu, lens = ctx.cu_tokens.tolist(), ctx.context_lens.tolist()
+    q = torch.cat((q_lat.float(), q_rot.float()), dim=-1)
+    for r in range(len(lens)):
+        t0, t1, n = cu[r], cu[r + 1], lens[r]
+        rows = plane[page_table[r, : -(-n // page_size)].long()].float().reshape(-1, plane.shape[2])[:n]
+        k = rows[:, None, :].expand(n, heads, rows.shape[1])
+        out[t0:t1] = _attend(q[t0:t1], k, k[..., :rank], n - (t1 - t0), scale, window, None).to(out.dtype)
+    return out
+
+
+def biased_paged_attention(qkv, pool, page_table, ctx, *, num_heads, num_kv_heads, key_dim, value_dim, scale, window=None, slopes=None):
+    H, KV = num_heads, num_kv_heads
+    page_size = pool.shape[3]
+    out = torch.empty((qkv.shape[0], H * value_dim), dtype=qkv.dtype, device=qkv.device)
+    cu, lens = ctx.cu_tokens.tolist(), ctx.context_lens.tolist()
+    for r in range(len(lens)):
+        t0, t1, n = cu[r], cu[r + 1], lens[r]
+        pages = page_table[r, : -(-n // page_size)].long()
+        k = pool[pages, 0].float().permute(0, 2, 1, 3).reshape(-1, KV, pool.shape[4])[:n, :, :key_dim]
+        v = pool[pages, 1].float().permute(0, 2, 1, 3).reshape(-1, KV, pool.shape[4])[:n, :, :value_dim]
+        q = qkv[t0:t1, : H * key_dim].float().view(t1 - t0, H, key_dim)
+        k, v = k.repeat_interleave(H // KV, dim=1), v.repeat_interleave(H // KV, dim=1)
+        out[t0:t1] = _attend(q, k, v, n - (t1 - t0), scale, window, slopes).reshape(t1 - t0, -1).to(out.dtype)
+    return out
+
+
 ALL = (
+    "group_rmsnorm",
+    "stream_inject",
+    "unary",
+    "linear_act",
+    "gate_mul",
+    "mingru_scan",
+    "latent_prepare",
+    "unit_norm_kv_write",
+    "head_linear",
+    "latent_paged_attention",
+    "biased_paged_attention",
     "embed",
     "rmsnorm",
     "linear",
