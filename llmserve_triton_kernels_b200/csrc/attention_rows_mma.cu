@@ -1,0 +1,342 @@
+// Attention in its general form on the tensor cores (bfloat16, mma.sync m16n8k16, 32-bit accumulation): queries in one or
+// two runs of lanes, keys of dk lanes and values of dv lanes addressed by strides (the values may be the head of the key
+// rows: a cached latent that is key and value at once then crosses shared memory once), an optional distance bias per
+// head, a window.  Prompt portions and decoded tokens take the same kernel.
+//
+// One CTA of four warps owns 64 rows of one (request, key/value head): a row is a (token, group member) pair, so the
+// heads that share keys sit side by side in a tile (with one key/value head for all query heads, a decoded token alone
+// fills heads-many rows).  Each warp keeps 16 rows: scores of a tile of keys in registers, the online softmax in 32-bit,
+// the probabilities straight from the score registers as the next product's left operand, the output in registers.
+// Key tiles (64 keys, or 32 where rows are long) arrive by cp.async into a ring of two; keys past the request's length
+// are filled with zeros.  The keys of a row tile may be cut over `splits` CTAs, whose partial results (unnormalised
+// output, running maximum, sum) a second kernel merges.
+#include "attention_rows.cuh"
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+constexpr int BM = 64, WARPS = 4, THREADS = WARPS * 32, PAD = 8;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const bf16* p) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const bf16* p) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(bf16* dst, const bf16* src, bool valid) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros and the source is not read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(addr), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ unsigned pack2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned*>(&v);
+}
+
+template <int DV_MAX, int BN>
+__global__ void __launch_bounds__(THREADS)
+attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int dk = a.d0 + a.d1, dv = a.dv, kp = dk + PAD, vp = dv + PAD;
+    const bool alias = a.values == a.keys && a.v_page == a.k_page && a.v_head == a.k_head && a.v_token == a.k_token;
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);  // [BM][kp]
+    bf16* Ks = Qs + BM * kp;                       // [2][BN][kp]
+    bf16* Vs = alias ? Ks : Ks + 2 * BN * kp;      // [2][BN][vp] unless the values are the head of the key rows
+    const int v_pitch = alias ? kp : vp, v_stage = alias ? BN * kp : BN * vp;
+
+    const int r = blockIdx.z, kvh = blockIdx.y;
+    const int tile = blockIdx.x / splits, split = blockIdx.x - tile * splits;
+    const int group = a.H / a.KV;
+    const int q_begin = a.cu_tokens[r], q_len = a.cu_tokens[r + 1] - q_begin, ctx_len = a.ctx_lens[r];
+    const int rows_total = q_len * group, row0 = tile * BM;
+    if (row0 >= rows_total) return;
+    const int first_pos = ctx_len - q_len;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    // the keys this tile's rows see, and this split's share of their tiles
+    const int pos_min = first_pos + row0 / group, pos_max = first_pos + min(rows_total - 1, row0 + BM - 1) / group;
+    const int key_lo = a.window > 0 ? max(0, pos_min - a.window + 1) : 0;
+    const int j_first = (key_lo / BN) * BN;
+    const int n_tiles = (pos_max - j_first) / BN + 1;
+    const int per = (n_tiles + splits - 1) / splits;
+    const int t_begin = split * per, t_end = min(n_tiles, t_begin + per);
+
+    const int* table = a.page_table + (size_t)r * a.table_width;
+    const int k_chunks = dk >> 3, v_chunks = dv >> 3;
+    auto load_tile = [&](int t, int stage) {
+        const int j0 = j_first + t * BN;
+        bf16* kd = Ks + stage * BN * kp;
+        for (int i = tid; i < BN * k_chunks; i += THREADS) {
+            const int key = i / k_chunks, c = i - key * k_chunks, j = j0 + key;
+            const bool valid = j < ctx_len;
+            const bf16* src = a.keys;
+            if (valid) src += (long long)table[j / a.page_size] * a.k_page + (long long)kvh * a.k_head + (long long)(j % a.page_size) * a.k_token + c * 8;
+            cp_async16(kd + key * kp + c * 8, src, valid);
+        }
+        if (!alias) {
+            bf16* vd = Vs + stage * BN * vp;
+            for (int i = tid; i < BN * v_chunks; i += THREADS) {
+                const int key = i / v_chunks, c = i - key * v_chunks, j = j0 + key;
+                const bool valid = j < ctx_len;
+                const bf16* src = a.values;
+                if (valid) src += (long long)table[j / a.page_size] * a.v_page + (long long)kvh * a.v_head + (long long)(j % a.page_size) * a.v_token + c * 8;
+                cp_async16(vd + key * vp + c * 8, src, valid);
+            }
+        }
+    };
+
+    // queries of the tile's rows into shared memory (rows past the request's last are zeros)
+    for (int i = tid; i < BM * k_chunks; i += THREADS) {
+        const int row = i / k_chunks, c = (i - row * k_chunks) * 8, R = row0 + row;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (R < rows_total) {
+            const int t = q_begin + R / group, h = kvh * group + R % group;
+            const bf16* src = c < a.d0 ? a.q0 + (long long)t * a.q0_token + (long long)h * a.q0_head + c
+                                       : a.q1 + (long long)t * a.q1_token + (long long)h * a.q1_head + (c - a.d0);
+            v = *reinterpret_cast<const uint4*>(src);
+        }
+        *reinterpret_cast<uint4*>(Qs + row * kp + c) = v;
+    }
+    if (t_begin < t_end) load_tile(t_begin, 0);
+    cp_async_commit();
+
+    // the two rows of this thread: (lane / 4) and (lane / 4 + 8) of the warp's sixteen
+    int pos[2], lo[2];
+    float slope[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int R = min(row0 + warp * 16 + (lane >> 2) + 8 * e, rows_total - 1);
+        pos[e] = first_pos + R / group;
+        lo[e] = a.window > 0 ? max(0, pos[e] - a.window + 1) : 0;
+        slope[e] = a.slopes ? a.slopes[kvh * group + R % group] : 0.f;
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[DV_MAX / 8][4];
+#pragma unroll
+    for (int i = 0; i < DV_MAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+    for (int t = t_begin; t < t_end; ++t) {
+        const int stage = (t - t_begin) & 1;
+        if (t + 1 < t_end) load_tile(t + 1, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const bf16* kt = Ks + stage * BN * kp;
+        const bf16* vt = Vs + stage * v_stage;
+        const int j0 = j_first + t * BN;
+
+        float s[BN / 8][4];
+#pragma unroll
+        for (int i = 0; i < BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+        for (int ks = 0; ks < dk; ks += 16) {
+            unsigned qa[4];
+            ldmatrix_x4(qa, Qs + (warp * 16 + (lane & 15)) * kp + ks + (lane >> 4) * 8);
+#pragma unroll
+            for (int nb = 0; nb < BN / 8; nb += 2) {
+                unsigned kb[4];
+                ldmatrix_x4(kb, kt + (nb * 8 + (lane >> 4) * 8 + (lane & 7)) * kp + ks + ((lane >> 3) & 1) * 8);
+                mma_bf16(s[nb], qa, kb[0], kb[1]);
+                mma_bf16(s[nb + 1], qa, kb[2], kb[3]);
+            }
+        }
+        // scale, bias, mask; the tile's maximum per row
+        float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nb = 0; nb < BN / 8; ++nb)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int e = c >> 1, j = j0 + nb * 8 + (lane & 3) * 2 + (c & 1);
+                float v = s[nb][c] * a.scale - slope[e] * (float)(pos[e] - j);
+                v = (j >= lo[e] && j <= pos[e]) ? v : -INFINITY;
+                s[nb][c] = v;
+                tile_max[e] = fmaxf(tile_max[e], v);
+            }
+        float rescale[2], m_use[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            tile_max[e] = fmaxf(tile_max[e], __shfl_xor_sync(0xffffffffu, tile_max[e], 1));
+            tile_max[e] = fmaxf(tile_max[e], __shfl_xor_sync(0xffffffffu, tile_max[e], 2));
+            const float m_new = fmaxf(m[e], tile_max[e]);
+            m_use[e] = m_new == -INFINITY ? 0.f : m_new;  // a row that has seen no key yet
+            rescale[e] = exp2f((m[e] - m_use[e]) * LOG2E);
+            m[e] = m_new;
+            l[e] *= rescale[e];
+        }
+#pragma unroll
+        for (int i = 0; i < DV_MAX / 8; ++i)
+            if (i * 8 < dv) {
+                o[i][0] *= rescale[0]; o[i][1] *= rescale[0];
+                o[i][2] *= rescale[1]; o[i][3] *= rescale[1];
+            }
+#pragma unroll
+        for (int nb = 0; nb < BN / 8; ++nb)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float p = exp2f((s[nb][c] - m_use[c >> 1]) * LOG2E);
+                s[nb][c] = p;
+                l[c >> 1] += p;
+            }
+        // O += P V
+#pragma unroll
+        for (int kb = 0; kb < BN / 16; ++kb) {
+            unsigned pa[4];
+            pa[0] = pack2(s[2 * kb][0], s[2 * kb][1]);
+            pa[1] = pack2(s[2 * kb][2], s[2 * kb][3]);
+            pa[2] = pack2(s[2 * kb + 1][0], s[2 * kb + 1][1]);
+            pa[3] = pack2(s[2 * kb + 1][2], s[2 * kb + 1][3]);
+#pragma unroll
+            for (int nb = 0; nb < DV_MAX / 8; nb += 2)
+                if (nb * 8 < dv) {
+                    unsigned vb[4];
+                    ldmatrix_x4_trans(vb, vt + (kb * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * v_pitch + nb * 8 + (lane >> 4) * 8);
+                    mma_bf16(o[nb], pa, vb[0], vb[1]);
+                    mma_bf16(o[nb + 1], pa, vb[2], vb[3]);
+                }
+        }
+        __syncthreads();  // the stage is free for the tile after next
+    }
+    cp_async_wait<0>();
+
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        l[e] += __shfl_xor_sync(0xffffffffu, l[e], 1);
+        l[e] += __shfl_xor_sync(0xffffffffu, l[e], 2);
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int R = row0 + warp * 16 + (lane >> 2) + 8 * e;
+        if (R >= rows_total) continue;
+        const int t = q_begin + R / group, h = kvh * group + R % group;
+        if (splits == 1) {
+            const float inv = 1.f / l[e];
+            bf16* op = a.out + (long long)t * a.out_token + (long long)h * a.out_head;
+#pragma unroll
+            for (int i = 0; i < DV_MAX / 8; ++i)
+                if (i * 8 < dv) {
+                    const int col = i * 8 + (lane & 3) * 2;
+                    *reinterpret_cast<__nv_bfloat162*>(op + col) = __floats2bfloat162_rn(o[i][2 * e] * inv, o[i][2 * e + 1] * inv);
+                }
+        } else {
+            const size_t slot = ((size_t)t * a.H + h) * splits + split;
+            float* po = part_o + slot * dv;
+#pragma unroll
+            for (int i = 0; i < DV_MAX / 8; ++i)
+                if (i * 8 < dv) {
+                    const int col = i * 8 + (lane & 3) * 2;
+                    *reinterpret_cast<float2*>(po + col) = make_float2(o[i][2 * e], o[i][2 * e + 1]);
+                }
+            if ((lane & 3) == 0) {
+                part_ml[slot * 2] = m[e];
+                part_ml[slot * 2 + 1] = l[e];
+            }
+        }
+    }
+}
+
+// out[t, h] = sum_s exp(m_s - M) o_s / sum_s exp(m_s - M) l_s over the splits' partial results; one warp per (token, head)
+__global__ void __launch_bounds__(128)
+attention_rows_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
+                            long long out_token, long long out_head, int n_tokens, int H, int dv, int splits) {
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (item >= (long long)n_tokens * H) return;
+    const int t = (int)(item / H), h = (int)(item - (long long)t * H);
+    const float* ml = part_ml + (size_t)item * splits * 2;
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, ml[2 * s]);
+    float L = 0.f;
+    for (int s = 0; s < splits; ++s) L += ml[2 * s] == -INFINITY ? 0.f : exp2f((ml[2 * s] - M) * LOG2E) * ml[2 * s + 1];
+    const float inv = 1.f / L;
+    bf16* op = out + (long long)t * out_token + (long long)h * out_head;
+    for (int d = lane; d < dv; d += 32) {
+        float acc = 0.f;
+        for (int s = 0; s < splits; ++s)
+            if (ml[2 * s] != -INFINITY) acc += exp2f((ml[2 * s] - M) * LOG2E) * part_o[((size_t)item * splits + s) * dv + d];
+        op[d] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+template <int DV_MAX, int BN>
+int launch(const RowsArgs<bf16>& a, int requests, int max_query_len, int splits, float* part_o, float* part_ml, size_t smem,
+           cudaStream_t stream) {
+    auto kernel = attention_rows_mma_kernel<DV_MAX, BN>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const int group = a.H / a.KV;
+    const long long tiles = ((long long)max_query_len * group + BM - 1) / BM;
+    if (tiles * splits > 0x7fffffffLL || a.KV > 65535 || requests > 65535) return LLM_ERR_UNSUPPORTED;
+    kernel<<<dim3((unsigned)(tiles * splits), a.KV, requests), THREADS, smem, stream>>>(a, splits, part_o, part_ml);
+    return launch_status();
+}
+
+}  // namespace
+
+// As llm_attention_rows, for bfloat16 with every run of lanes a multiple of 16 and 16-byte aligned rows; dv <= 256.
+// `max_query_len`: the most tokens a request brings (it sizes the grid).  `splits` > 1 cuts every row tile's keys over
+// that many CTAs; part_o [n_tokens * H * splits * dv] and part_ml [n_tokens * H * splits * 2] (float32) then hold the
+// partial results until the merge that follows.  Returns LLM_ERR_UNSUPPORTED for shapes it does not take.
+LLM_EXPORT int llm_attention_rows_mma(const void* q0, long long q0_token, long long q0_head, int d0, const void* q1,
+                                      long long q1_token, long long q1_head, int d1, void* out, long long out_token,
+                                      long long out_head, const void* keys, long long k_page, long long k_head,
+                                      long long k_token, const void* values, long long v_page, long long v_head,
+                                      long long v_token, int dv, const int* page_table, int table_width,
+                                      const int* token_request, const int* cu_tokens, const int* ctx_lens, const float* slopes,
+                                      int n_tokens, int requests, int max_query_len, int H, int KV, int page_size, int window,
+                                      float scale, int splits, float* part_o, float* part_ml, cudaStream_t stream) {
+    if (n_tokens <= 0 || requests <= 0) return 0;
+    if (d0 <= 0 || d1 < 0 || dv <= 0 || H <= 0 || KV <= 0 || H % KV || page_size <= 0 || table_width <= 0 || splits < 1 ||
+        max_query_len < 1 || (d1 > 0 && q1 == nullptr) || (splits > 1 && (part_o == nullptr || part_ml == nullptr)))
+        return LLM_ERR_BAD_ARGUMENT;
+    const int dk = d0 + d1;
+    auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    if ((d0 & 15) || (d1 & 15) || (dv & 15) || dv > 256 || dk > 640) return LLM_ERR_UNSUPPORTED;
+    if ((q0_token & 7) || (q0_head & 7) || (q1_token & 7) || (q1_head & 7) || (k_page & 7) || (k_head & 7) || (k_token & 7) ||
+        (v_page & 7) || (v_head & 7) || (v_token & 7) || (out_token & 1) || (out_head & 1))
+        return LLM_ERR_UNSUPPORTED;
+    if (!aligned(q0) || (d1 > 0 && !aligned(q1)) || !aligned(keys) || !aligned(values) || ((uintptr_t)out & 3)) return LLM_ERR_UNSUPPORTED;
+    RowsArgs<bf16> a;
+    a.q0 = (const bf16*)q0; a.q1 = (const bf16*)q1;
+    a.q0_token = q0_token; a.q0_head = q0_head; a.q1_token = q1_token; a.q1_head = q1_head;
+    a.d0 = d0; a.d1 = d1;
+    a.out = (bf16*)out; a.out_token = out_token; a.out_head = out_head;
+    a.keys = (const bf16*)keys; a.values = (const bf16*)values;
+    a.k_page = k_page; a.k_head = k_head; a.k_token = k_token; a.v_page = v_page; a.v_head = v_head; a.v_token = v_token;
+    a.dv = dv;
+    a.page_table = page_table; a.token_request = token_request; a.cu_tokens = cu_tokens; a.ctx_lens = ctx_lens;
+    a.slopes = slopes;
+    a.table_width = table_width; a.n_tokens = n_tokens; a.H = H; a.KV = KV; a.page_size = page_size; a.window = window;
+    a.scale = scale;
+    const bool alias = values == keys && v_page == k_page && v_head == k_head && v_token == k_token;
+    auto smem_for = [&](int bn) { return (size_t)(BM + 2 * bn) * (dk + PAD) * 2 + (alias ? 0 : (size_t)2 * bn * (dv + PAD) * 2); };
+    const bool wide = smem_for(64) <= 160 * 1024;
+    const size_t smem = smem_for(wide ? 64 : 32);
+    if (smem > 220 * 1024) return LLM_ERR_UNSUPPORTED;
+    int code;
+    if (dv <= 64)
+        code = wide ? launch<64, 64>(a, requests, max_query_len, splits, part_o, part_ml, smem, stream)
+                    : launch<64, 32>(a, requests, max_query_len, splits, part_o, part_ml, smem, stream);
+    else if (dv <= 128)
+        code = wide ? launch<128, 64>(a, requests, max_query_len, splits, part_o, part_ml, smem, stream)
+                    : launch<128, 32>(a, requests, max_query_len, splits, part_o, part_ml, smem, stream);
+    else
+        code = wide ? launch<256, 64>(a, requests, max_query_len, splits, part_o, part_ml, smem, stream)
+                    : launch<256, 32>(a, requests, max_query_len, splits, part_o, part_ml, smem, stream);
+    if (code != 0 || splits == 1) return code;
+    const long long items = (long long)n_tokens * H;
+    attention_rows_merge_kernel<<<(unsigned)((items + 3) / 4), 128, 0, stream>>>(part_o, part_ml, (bf16*)out, out_token, out_head,
+                                                                                n_tokens, H, dv, splits);
+    return launch_status();
+}

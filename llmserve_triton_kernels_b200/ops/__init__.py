@@ -51,6 +51,8 @@ _SIGNATURES = {
     "llm_unit_norm_kv_write": [_vp, _i, _i, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "llm_attention_rows": [_vp, _ll, _ll, _i, _vp, _ll, _ll, _i, _vp, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _i, _i,
                            _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp],
+    "llm_attention_rows_mma": [_vp, _ll, _ll, _i, _vp, _ll, _ll, _i, _vp, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _i,
+                               _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp, _vp],
     "llm_gemm_simt_batched": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _vp],
     "llm_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
 }
@@ -968,6 +970,30 @@ def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, p
     if slopes is not None:
         _need(slopes.dtype == torch.float32 and slopes.numel() == num_heads and slopes.is_contiguous(), "slopes must be float32 [heads]")
     out = torch.empty((n, num_heads, value_dim), dtype=q0.dtype, device=q0.device)
+    if q0.dtype == torch.bfloat16 and not _FORCE_GENERIC_ATTENTION and d0 % 16 == 0 and d1 % 16 == 0 and value_dim % 16 == 0 and value_dim <= 256:
+        # the tensor cores: 64 rows of (token, group member) a CTA; few CTAs and long contexts: the keys cut over several
+        group = num_heads // num_kv_heads
+        longest = getattr(ctx, "max_context_len", None) or int(ctx.context_lens.max())
+        if window:
+            longest = min(longest, window + ctx.max_query_len)
+        ctas = -(-ctx.max_query_len * group // 64) * num_kv_heads * ctx.num_requests
+        splits = max(1, min(-(-longest // 256), _sm_count() // ctas, 16, _SPLIT_SCRATCH_BYTES // (n * num_heads * value_dim * 4)))
+        part_o = part_ml = None
+        if splits > 1:
+            part_o = torch.empty((n * num_heads * splits * value_dim,), dtype=torch.float32, device=q0.device)
+            part_ml = torch.empty((n * num_heads * splits * 2,), dtype=torch.float32, device=q0.device)
+        code = _launch(
+            "llm_attention_rows_mma", _ptr(q0), q0.stride(0), q0.stride(1), d0, _ptr(q1), 0 if q1 is None else q1.stride(0),
+            0 if q1 is None else q1.stride(1), d1, _ptr(out), out.stride(0), out.stride(1), keys, *k_strides, values, *v_strides,
+            value_dim, _ptr(page_table), page_table.shape[1], _ptr(ctx.token_request), _ptr(ctx.cu_tokens), _ptr(ctx.context_lens),
+            _ptr(slopes), n, ctx.num_requests, ctx.max_query_len, num_heads, num_kv_heads, page_size, int(window or 0), float(scale),
+            splits, _ptr(part_o), _ptr(part_ml), _stream(),
+        )
+        if code != 10002:
+            add_launches(int(splits > 1))
+            _check(code, "attention_rows (tensor cores)")
+            return out
+        add_launches(-1)  # a layout the kernel does not take: the general one below
     code = _launch(
         "llm_attention_rows", _ptr(q0), q0.stride(0), q0.stride(1), d0, _ptr(q1), 0 if q1 is None else q1.stride(0),
         0 if q1 is None else q1.stride(1), d1, _ptr(out), out.stride(0), out.stride(1), keys, *k_strides, values, *v_strides,

@@ -247,8 +247,8 @@ def _attend(q, k, v, first_pos, scale, window, slopes):
     """q [T, H, dk], k [n, H, dk], v [n, H, dv] float32; query t stands at position first_pos + t."""
     n = k.shape[0]
     s = torch.einsum("thd,jhd->htj", q, k) * scale
-    pos = torch.arange(first_pos, first_pos + q.shape[0])[:, None]
-    j = torch.arange(n)[None, :]
+    pos = torch.arange(first_pos, first_pos + q.shape[0], device=q.device)[:, None]
+    j = torch.arange(n, device=q.device)[None, :]
     if slopes is not None:
         s = s - slopes.float()[:, None, None] * (pos - j).float()
     visible = j <= pos

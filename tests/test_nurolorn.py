@@ -1,0 +1,298 @@
+"""The Nurolorn design in the engine against the plain implementation (tests/plain_nurolorn.py).
+
+Every test makes its own small configuration and random weights.  The engine runs the requests in some way of
+cutting the work (whole, token by token, in portions down to two tokens, in mixed batches over a pool so small that
+pages and state slots are used again) and the logits at every position are compared with the plain implementation's,
+which knows no cache.  On the GPU the engine's kernels run, in true 32-bit and in bfloat16; without one the same host
+logic runs over the plain operations.
+"""
+
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+import nurolorn_configs as configs
+import plain_nurolorn
+import plain_ops
+
+F32_TOL = 3e-5  # of the root mean square of the row's logits
+BF16_TOL = 4e-2
+
+WHERE = ["plain", pytest.param("cuda-float32", marks=pytest.mark.gpu), pytest.param("cuda-bfloat16", marks=pytest.mark.gpu)]
+
+
+def make_model(cfg_dict: dict, seed: int, where: str, std: float = 0.12):
+    import llmserve_triton_kernels_b200.models  # noqa: F401
+    from llmserve_triton_kernels_b200.config import architecture_of
+    from llmserve_triton_kernels_b200.models.model import Model
+    from llmserve_triton_kernels_b200.weights.random_init import random_tensors
+
+    device, dtype = ("cpu", "float32") if where == "plain" else ("cuda:0", where.split("-")[1])
+    arch = architecture_of(cfg_dict)
+    config = arch.config_class.from_dict(cfg_dict)
+    model = (arch.model_class or Model)(arch.plan(config), getattr(torch, dtype), device)
+    tensors = random_tensors(model.tensor_specs(), seed, std, torch.bfloat16)
+    model.bind(tensors)
+    return model, tensors, dtype
+
+
+@pytest.fixture
+def engine(monkeypatch):
+    """``engine(where)`` patches the plain operations in when there is no GPU to run on."""
+
+    def use(where: str):
+        if where == "plain":
+            from llmserve_triton_kernels_b200 import ops
+
+            for name in plain_ops.ALL:
+                monkeypatch.setattr(ops, name, getattr(plain_ops, name))
+
+    return use
+
+
+class Driver:
+    """Steps of ``[(request, tokens)]`` through the framework's step function; gathers logits by (request, position)."""
+
+    def __init__(self, model, num_pages: int, page_size: int = 4, max_requests: int = 4):
+        from llmserve_triton_kernels_b200.cache import CacheManager
+        from llmserve_triton_kernels_b200.engine.step import StepFunction
+
+        self.cache = CacheManager(model.cache_specs(), model.plan.schedule, page_size=page_size, num_pages=num_pages,
+                                  max_requests=max_requests, dtype=model.dtype, device=model.device)
+        self.step = StepFunction(model, self.cache)
+        self.fed: dict[str, int] = {}
+        self.got: dict[tuple[str, int], torch.Tensor] = {}
+
+    def run(self, entries, end=()):
+        from llmserve_triton_kernels_b200.engine.batch import StepEntry
+
+        logits = self.step([StepEntry(r, list(t), list(range(len(t)))) for r, t in entries]).float().cpu()
+        row = 0
+        for r, t in entries:
+            start = self.fed.get(r, 0)
+            for i in range(len(t)):
+                self.got[(r, start + i)] = logits[row].clone()
+                row += 1
+            self.fed[r] = start + len(t)
+        for r in end:
+            self.cache.free_request(r)
+            self.fed.pop(r)
+        self.cache.check()
+
+
+def check(got, expected, dtype: str, what: str = ""):
+    tol = F32_TOL if dtype == "float32" else BF16_TOL
+    for (req, pos), row in sorted(got.items()):
+        ref = expected[req.split("#")[0]][pos].float()
+        assert torch.isfinite(row).all(), f"{what}: non-finite logits at request {req!r} position {pos}"
+        d = row - ref
+        err = float((d - d.mean()).pow(2).mean().sqrt() / ref.pow(2).mean().sqrt().clamp_min(1e-6))
+        assert err <= tol, f"{what}: first wrong row: request {req!r} position {pos}: error {err:.3e} > {tol:.1e}"
+
+
+def tokens_for(vocab: int, lengths, seed: int):
+    g = torch.Generator().manual_seed(seed)
+    return {f"r{i}": torch.randint(0, vocab, (n,), generator=g).tolist() for i, n in enumerate(lengths)}
+
+
+def expected_of(cfg, tensors, requests):
+    return {r: plain_nurolorn.forward(cfg, tensors, t) for r, t in requests.items()}
+
+
+# --------------------------------------------------------------------------------------------- mechanisms alone
+ALONE = {
+    "latent": configs.config([configs.latent(3, 8, 6, 10, 14, 0.3, base=50.0, dims=4)], width=32, groups=2),
+    "latent_16": configs.config([configs.latent(4, 16, 16, 32, 48, 0.3, base=50.0)], width=32, groups=1),
+    "mingru": configs.config([configs.mingru(24)], width=32, groups=2),
+    "window": configs.config([configs.window(4, 2, 10, 6, 7, 0.5)], width=32, groups=4),
+    "window_16": configs.config([configs.window(4, 1, 16, 32, 9, 0.5)], width=32, groups=4),
+    "mlp": configs.config([configs.mingru(8, ff=40)], width=32, groups=1, mult=1.0),
+}
+
+
+@pytest.mark.parametrize("where", WHERE)
+@pytest.mark.parametrize("name", sorted(ALONE))
+def test_each_mixer_alone_whole_and_token_by_token(name, where, engine):
+    """One layer of one kind: the whole prompt in one step, and the same tokens one by one through the cache or state."""
+    engine(where)
+    cfg = ALONE[name]
+    model, tensors, dtype = make_model(cfg, 11, where, std=0.2)
+    reqs = tokens_for(cfg["vocab"], [37], 5)
+    exp = expected_of(cfg, tensors, reqs)
+    d = Driver(model, num_pages=24)
+    d.run([("r0", reqs["r0"])], end=["r0"])
+    check(d.got, exp, dtype, "whole")
+    d.got.clear()
+    for i, t in enumerate(reqs["r0"]):
+        d.run([("r0", [t])], end=["r0"] if i == len(reqs["r0"]) - 1 else [])
+    check(d.got, exp, dtype, "token by token")
+
+
+@pytest.mark.parametrize("where", WHERE)
+def test_residual_stream_after_every_layer(where, engine):
+    """The stream after every entry of the order (a looped layer counts each time), as the layer probe shows it."""
+    engine(where)
+    cfg = configs.ODD
+    model, tensors, dtype = make_model(cfg, 3, where)
+    tokens = tokens_for(cfg["vocab"], [19], 2)["r0"]
+    _, layers = plain_nurolorn.forward(cfg, tensors, tokens, return_layers=True)
+    seen = []
+    model.layer_probe = lambda i, x: seen.append(x.float().cpu().clone())
+    Driver(model, num_pages=16).run([("r0", tokens)], end=["r0"])
+    assert len(seen) == layers.shape[0] == 1 + 2 * 3 + 1
+    tol = 1e-4 if dtype == "float32" else 6e-2
+    for i, x in enumerate(seen):
+        scale = float(layers[i].abs().max())
+        assert float((x - layers[i].float()).abs().max()) <= tol * scale, f"the stream differs after entry {i} of the order"
+
+
+# --------------------------------------------------------------------------------------------- ways of cutting
+@pytest.mark.parametrize("where", WHERE)
+@pytest.mark.parametrize("name", sorted(configs.ALL))
+def test_ways_of_cutting(name, where, engine):
+    """Whole prompts; a prompt then its last tokens one by one; portions of changing size down to two tokens and one;
+    the first tokens of a sequence alone."""
+    engine(where)
+    cfg = configs.ALL[name]
+    model, tensors, dtype = make_model(cfg, 7, where)
+    reqs = tokens_for(cfg["vocab"], [1, 2, 45, 83], 9)
+    exp = expected_of(cfg, tensors, reqs)
+    d = Driver(model, num_pages=24)
+    for r, t in reqs.items():
+        d.run([(r, t)], end=[r])
+    check(d.got, exp, dtype, "whole")
+    d.got.clear()
+    t = reqs["r3"]
+    d.run([("r3", t[:40])])
+    for i in range(40, len(t)):
+        d.run([("r3", [t[i]])], end=["r3"] if i == len(t) - 1 else [])
+    check(d.got, exp, dtype, "decode")
+    d.got.clear()
+    for r in ("r2", "r3"):
+        t, i, k = reqs[r], 0, 0
+        sizes = (1, 2, 7, 2, 16, 3, 5, 2, 1, 9)
+        while i < len(t):
+            n = min(sizes[k % len(sizes)], len(t) - i)
+            d.run([(r, t[i : i + n])], end=[r] if i + n == len(t) else [])
+            i, k = i + n, k + 1
+    check(d.got, exp, dtype, "portions")
+
+
+@pytest.mark.parametrize("where", WHERE)
+@pytest.mark.parametrize("name", ["odd", "head_loop"])
+def test_mixed_batches_with_pages_and_slots_used_again(name, where, engine):
+    """Up to four unequal requests a step, portions beside single tokens, over a pool of few pages and four state
+    slots: every request's logits equal those of the request alone, also on pages and slots that others gave back."""
+    engine(where)
+    cfg = configs.ALL[name]
+    model, tensors, dtype = make_model(cfg, 13, where)
+    base = tokens_for(cfg["vocab"], [50, 9, 31, 64, 3, 40], 21)
+    exp = expected_of(cfg, tensors, base)
+    reqs = {**base, **{r + "#2": t for r, t in base.items()}}  # each once more, on used pages and slots
+    prefill = {r: max(1, len(t) - 6) for r, t in reqs.items()}
+    d = Driver(model, num_pages=52, page_size=4, max_requests=4)
+    waiting, live = list(reqs), {}
+    while waiting or live:
+        if waiting and len(live) < 4:
+            live[waiting.pop(0)] = 0
+        entries, end = [], []
+        for r, fed in list(live.items()):
+            t = reqs[r]
+            n = min(7, prefill[r] - fed) if fed < prefill[r] else 1
+            n = min(n, len(t) - fed)
+            entries.append((r, t[fed : fed + n]))
+            live[r] = fed + n
+            if live[r] == len(t):
+                end.append(r)
+                del live[r]
+        d.run(entries, end=end)
+    assert len({k[0] for k in d.got}) == len(reqs)
+    check(d.got, exp, dtype, "mixed")
+    assert d.cache.slots.num_used == 0 and all(g.allocator.num_used == 0 for g in d.cache.groups)
+
+
+@pytest.mark.parametrize("where", WHERE)
+def test_long_decoding_past_windows_and_pages(where, engine):
+    """A short prompt, then many tokens one by one: the window passes over decoded tokens, pages fill and are given
+    back, the recurrent state is carried far."""
+    engine(where)
+    cfg = configs.HEAD_LOOP
+    model, tensors, dtype = make_model(cfg, 17, where)
+    t = tokens_for(cfg["vocab"], [150], 4)["r0"]
+    exp = expected_of(cfg, tensors, {"r0": t})
+    d = Driver(model, num_pages=40, page_size=4)
+    d.run([("r0", t[:3])])
+    for i in range(3, len(t)):
+        d.run([("r0", [t[i]])], end=["r0"] if i == len(t) - 1 else [])
+    check(d.got, exp, dtype, "long decoding")
+    windowed = [g for g in d.cache.groups if g.spec.window is not None]
+    assert windowed, "the configuration has a windowed layer"
+
+
+# --------------------------------------------------------------------------------------------- generation
+@pytest.mark.parametrize("where", WHERE)
+def test_greedy_generation_through_the_scheduler(where, engine, monkeypatch):
+    """``LLM.generate`` with greedy sampling, several prompts at once in portions: every chosen token is the plain
+    implementation's choice given the tokens before it (or its logit is within rounding of the best)."""
+    engine(where)
+    if where == "plain":
+        from llmserve_triton_kernels_b200 import ops
+
+        monkeypatch.setattr(ops, "argmax", plain_ops.argmax)
+        monkeypatch.setattr(ops, "sample", plain_ops.sample)
+    from llmserve_triton_kernels_b200.engine.llm import LLM
+    from llmserve_triton_kernels_b200.sampling import SamplingParams
+    from llmserve_triton_kernels_b200.weights.random_init import random_tensors
+
+    cfg = configs.HEAD_LOOP
+    device, dtype = ("cpu", "float32") if where == "plain" else ("cuda:0", where.split("-")[1])
+    llm = LLM(cfg, dtype=dtype, device=device, seed=5, block_size=4, num_blocks=60, max_batch_size=3, chunk_size=6,
+              max_num_batched_tokens=16, freeze_gc=False)
+    tensors = random_tensors(llm.model.tensor_specs(), 5, 0.02, torch.bfloat16)
+    prompts = list(tokens_for(cfg["vocab"], [5, 17, 9, 2], 8).values())
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=12))
+    assert [len(o.token_ids) for o in outs] == [12] * 4
+    for prompt, o in zip(prompts, outs):
+        logits = plain_nurolorn.forward(cfg, tensors, prompt + o.token_ids)
+        for k, tok in enumerate(o.token_ids):
+            row = logits[len(prompt) + k - 1]
+            slack = 1e-4 if dtype == "float32" else 0.05
+            assert float(row.max() - row[tok]) <= slack * float(row.abs().max()), f"token {k} of a request is not the greedy choice"
+
+
+# --------------------------------------------------------------------------------------------- configuration
+def test_configuration_is_read_from_the_dictionary_and_written_back():
+    from llmserve_triton_kernels_b200.config import ConfigError, NurolornConfig, architecture_of
+
+    for cfg in configs.ALL.values():
+        assert architecture_of(cfg).name == "Nurolorn"
+        c = NurolornConfig.from_dict(cfg)
+        assert NurolornConfig.from_dict(c.to_dict()) == c
+    bad = {**configs.ODD, "layers": [{"type": "convolution", "mixer": {}, "mlp": None}]}
+    with pytest.raises(ConfigError, match="convolution"):
+        NurolornConfig.from_dict(bad)
+    with pytest.raises(ConfigError, match="loop"):
+        NurolornConfig.from_dict({**configs.ODD, "loop": {"start": 2, "stop": 9, "times": 2}})
+    with pytest.raises(ConfigError, match="groups"):
+        NurolornConfig.from_dict({**configs.ODD, "norm": {"eps": 1e-5, "groups": 5}})
+
+
+def test_plan_orders_a_loop_with_caches_of_its_own_and_names_every_tensor():
+    import llmserve_triton_kernels_b200.models  # noqa: F401
+    from llmserve_triton_kernels_b200.config import NurolornConfig
+    from llmserve_triton_kernels_b200.models.model import Model
+    from llmserve_triton_kernels_b200.models.nurolorn import nurolorn_plan
+
+    plan = nurolorn_plan(NurolornConfig.from_dict(configs.ODD))
+    assert [r.layer for r in plan.schedule] == [0, 1, 2, 1, 2, 1, 2, 3]
+    assert [(i.before, i.add_embedding, i.row) for i in plan.injections] == [(1, False, 0), (3, True, 1), (5, True, 2)]
+    model = Model(plan, torch.float32, "cpu")
+    names = set(model.tensor_specs())
+    assert {"embed", "head", "final.norm", "loop.step", "l0.norm1", "l0.norm2", "l0.mix.z.b", "l1.mix.dkv.norm", "l2.mix.k", "l3.mlp.down"} <= names
+    assert "l1.norm2" not in names  # a layer without a feed-forward
+    specs = model.cache_specs()
+    assert len(specs) == 8 and len({id(s) for s in specs}) == 8
+    assert model.graph_safe

@@ -152,7 +152,7 @@ def run_trace(model_dir, dtype: str, trace: Trace, out_dir, max_tokens: int | No
         if proc.poll() is None:
             proc.kill()
     cfg = json.loads((Path(model_dir) / "config.json").read_text())
-    vocab = cfg["vocab_size"]
+    vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
     got: dict[tuple[str, int], np.ndarray] = {}
     for s in trace.steps:
         rows = trace.rows.get(s["step"])
