@@ -190,6 +190,196 @@ def prefill_flops(cfg, tokens: int) -> float:
     return gemm + attention
 
 
+def design_comparison(args) -> int:
+    """Prefill and decode of a Nurolorn preset beside a Llama twin (the same width, as many layers as the design runs
+    entries of its order, a SwiGLU feed-forward of the same parameter count, vocabulary and head size alike), both with
+    random weights, through the same step function; then the design's kernels one by one against their rooflines.
+    Every timed launch follows a write of 256 MB (larger than L2); times are CUDA events on the launching stream."""
+    import torch
+
+    from llmserve_triton_kernels_b200 import models as _models  # noqa: F401
+    from llmserve_triton_kernels_b200 import ops
+    from llmserve_triton_kernels_b200.cache import CacheManager
+    from llmserve_triton_kernels_b200.config import architecture_of
+    from llmserve_triton_kernels_b200.config.presets import PRESETS
+    from llmserve_triton_kernels_b200.engine.batch import StepEntry
+    from llmserve_triton_kernels_b200.engine.step import StepFunction
+    from llmserve_triton_kernels_b200.models.load import random_model
+
+    peaks, peaks_from = load_peaks()
+    device = "cuda:0"
+    torch.cuda.set_device(device)
+    design = dict(PRESETS[args.design])
+    arch = architecture_of(design)
+    dcfg = arch.config_class.from_dict(design)
+    entries = len(arch.plan(dcfg).schedule)
+    width, ff, vocab = design["width"], design["layers"][0]["mlp"]["ff"], design["vocab"]
+    twin = {
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_act": "silu", "rope_theta": 10000.0, "rms_norm_eps": 1e-5,
+        "tie_word_embeddings": False, "vocab_size": vocab, "hidden_size": width, "intermediate_size": (ff * 2 // 3 + 63) // 64 * 64,
+        "num_hidden_layers": entries, "num_attention_heads": width // 64, "num_key_value_heads": max(1, width // 512),
+        "max_position_embeddings": 8192,
+    }
+    flush = torch.empty(256 * 2**20, dtype=torch.uint8, device=device)
+    steps = max(3, min(args.steps, 50))
+
+    def timed(fn, n=steps, setup=None):
+        total = 0.0
+        for i in range(args.warmup + n):
+            if setup is not None:
+                setup()
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            b.synchronize()
+            if i >= args.warmup:
+                total += a.elapsed_time(b)
+        return total / n * 1e3  # microseconds
+
+    def tokens(n, seed):
+        g = torch.Generator().manual_seed(seed)
+        return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+    out = {"design": args.design, "peaks_from": peaks_from, "models": {}}
+    for name, cfg_dict in ((args.design, design), ("llama-twin", twin)):
+        a = architecture_of(cfg_dict)
+        model = random_model(a.config_class.from_dict(cfg_dict), 0, "bfloat16", device)
+        cache = CacheManager(model.cache_specs(), model.plan.schedule, page_size=16, num_pages=8 * 200 + 64, max_requests=8,
+                             dtype=torch.bfloat16, device=device)
+        step = StepFunction(model, cache)
+        res = {"weight_GB": round(model.weight_bytes() / 1e9, 3), "entries_of_the_order": len(model.plan.schedule)}
+        for n in (512, 2048):
+            toks = tokens(n, n)
+
+            def prefill():
+                step([StepEntry("p", toks, [n - 1])])
+
+            def done():
+                if cache.has_request("p"):
+                    cache.free_request("p")
+
+            us = timed(prefill, setup=done)
+            done()
+            res[f"prefill_{n}"] = {"ms": round(us / 1e3, 3), "tok_s": round(n / us * 1e6)}
+        for batch in (1, 8):
+            reqs = [f"d{i}" for i in range(batch)]
+            step([StepEntry(r, tokens(512, 7 + i), [511]) for i, r in enumerate(reqs)])
+            nxt = tokens(batch, 99)
+            us = timed(lambda: step([StepEntry(r, [t], [0]) for r, t in zip(reqs, nxt)]), n=min(100, 8 * steps))
+            for r in reqs:
+                cache.free_request(r)
+            bytes_read = model.weight_bytes() + cache.nbytes() * 0  # weights dominate at 512 tokens of context
+            res[f"decode_batch{batch}_ctx512"] = {"ms_per_step": round(us / 1e3, 4), "tok_s": round(batch / us * 1e6),
+                                                  "of_hbm_peak_weights_only": round(bytes_read / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 3)}
+        out["models"][name] = res
+        del step, cache, model
+        torch.cuda.empty_cache()
+
+    # the design's own kernels, alone, at the preset's sizes: 2,048 prompt tokens of one request, and 8 decoding requests
+    # of 2,048 cached tokens; a Llama layer's like kernel beside each
+    from types import SimpleNamespace
+
+    def i32(x):
+        return torch.tensor(x, dtype=torch.int32, device=device)
+
+    def ctx_for(query_lens, context_lens, page_size=16):
+        cu = [0]
+        for q in query_lens:
+            cu.append(cu[-1] + q)
+        width_ = max(-(-c // page_size) for c in context_lens)
+        table, page = torch.zeros((len(query_lens), width_), dtype=torch.int32), 0
+        owner, pos, slots = [], [], []
+        for r, (q, c) in enumerate(zip(query_lens, context_lens)):
+            pages = list(range(page, page + -(-c // page_size)))
+            page += len(pages)
+            table[r, : len(pages)] = torch.tensor(pages, dtype=torch.int32)
+            owner += [r] * q
+            pos += list(range(c - q, c))
+            slots += [pages[p // page_size] * page_size + p % page_size for p in range(c - q, c)]
+        ctx = SimpleNamespace(num_tokens=cu[-1], num_requests=len(query_lens), token_request=i32(owner), cu_tokens=i32(cu),
+                              context_lens=i32(context_lens), positions=i32(pos), max_query_len=max(query_lens),
+                              max_context_len=max(context_lens), host_cu_tokens=cu)
+        return ctx, table.to(device), i32(slots), page
+
+    L = next(x["mixer"] for x in design["layers"] if x["type"] == "latent_attention")
+    W = next(x["mixer"] for x in design["layers"] if x["type"] == "attention")
+    H, rank, rot, hd = L["heads"], L["kv_rank"], L["rot_dim"], L["dim"]
+    bf = torch.bfloat16
+    kernels = {}
+
+    def hbm(name, us, nbytes, like=None):
+        kernels[name] = {"us": round(us, 2), "GB_s": round(nbytes / us / 1e3), "of_hbm_peak": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 3)}
+        if like:
+            kernels[name]["like"] = like
+
+    def tensor(name, us, flops, like=None):
+        kernels[name] = {"us": round(us, 2), "TFLOP_s": round(flops / us / 1e6, 1), "of_bf16_peak": round(flops / us / 1e6 / peaks["bf16_tflops"], 3)}
+        if like:
+            kernels[name]["like"] = like
+
+    for label, qs, cs in (("prefill_2048", [2048], [2048]), ("decode_8x2048", [1] * 8, [2048] * 8)):
+        ctx, table, slots, pages = ctx_for(qs, cs)
+        n = ctx.num_tokens
+        pairs = sum(q * c - q * (q - 1) // 2 for q, c in zip(qs, cs))
+        plane = torch.randn(pages, 16, rank + rot, device=device).to(bf)
+        q_lat, q_rot = torch.randn(n, H, rank, device=device).to(bf) * 0.1, torch.randn(n, H, rot, device=device).to(bf) * 0.1
+        us = timed(lambda: ops.latent_paged_attention(q_lat, q_rot, plane, table, ctx, rank=rank, scale=0.1))
+        if label.startswith("prefill"):
+            tensor(f"latent_attention_{label}", us, 2.0 * H * (2 * rank + rot) * pairs, like="Llama prefill attention (tcgen05)")
+        else:
+            hbm(f"latent_attention_{label}", us, sum(cs) * (rank + rot) * 2, like="Llama decode attention (split keys)")
+        KV, win = W["kv_heads"], W["mask"]["size"]
+        pool = torch.randn(pages, 2, KV, 16, hd, device=device).to(bf)
+        qkv = torch.randn(n, (W["heads"] + 2 * KV) * hd, device=device).to(bf)
+        slopes = torch.pow(2.0, -8.0 * torch.arange(1, W["heads"] + 1) / W["heads"]).float().to(device)
+        kw = dict(num_heads=W["heads"], num_kv_heads=KV, key_dim=hd, value_dim=hd, scale=0.1, window=win, slopes=slopes)
+        us = timed(lambda: ops.biased_paged_attention(qkv, pool, table, ctx, **kw))
+        seen = sum(min(win, p + 1) for q, c in zip(qs, cs) for p in range(c - q, c))
+        if label.startswith("prefill"):
+            tensor(f"window_attention_{label}", us, 4.0 * W["heads"] * hd * seen, like="Llama prefill attention (tcgen05)")
+        else:
+            hbm(f"window_attention_{label}", us, len(qs) * min(win, cs[0]) * 2 * KV * hd * 2, like="Llama decode attention (split keys)")
+        # the Llama twin's attention on the same tokens
+        tH, tKV = twin["num_attention_heads"], twin["num_key_value_heads"]
+        tpool = torch.randn(pages, 2, tKV, 16, 64, device=device).to(bf)
+        tq = torch.randn(n, (tH + 2 * tKV) * 64, device=device).to(bf)
+        us = timed(lambda: ops.paged_attention(tq, tpool, table, ctx, num_heads=tH, num_kv_heads=tKV, head_dim=64, scale=0.125))
+        if label.startswith("prefill"):
+            tensor(f"llama_attention_{label}", us, 4.0 * tH * 64 * pairs)
+        else:
+            hbm(f"llama_attention_{label}", us, sum(cs) * 2 * tKV * 64 * 2)
+        # row-wise kernels
+        gw = next(x["mixer"]["width"] for x in design["layers"] if x["type"] == "mingru")
+        proj = torch.randn(n, 3 * gw, device=device)
+        states, sl = torch.zeros(8, gw, device=device), i32(list(range(len(qs))))
+        us = timed(lambda: ops.mingru_scan(proj, None, None, states, sl, ctx.cu_tokens, len(qs), gw, bf, max(qs)))
+        hbm(f"mingru_scan_{label}", us, n * gw * (12 + 2), like="(no like kernel in Llama)")
+        resid, delta, wn = torch.randn(n, width, device=device), torch.randn(n, width, device=device), torch.ones(width, device=device)
+        us = timed(lambda: ops.group_rmsnorm(resid, wn, 1e-6, 2, delta=delta, alpha=0.7, out_dtype=bf))
+        hbm(f"group_rmsnorm_{label}", us, n * width * (4 + 4 + 4 + 2), like="llama_rmsnorm")
+        us = timed(lambda: ops.rmsnorm(resid, wn, 1e-6, delta=delta, out_dtype=bf))
+        hbm(f"llama_rmsnorm_{label}", us, n * width * (4 + 4 + 4 + 2))
+        stacked = torch.randn(n, H * (hd + rot) + rank + rot + H * hd, device=device).to(bf)
+        freq = torch.ones(rot // 2, device=device)
+        us = timed(lambda: ops.latent_prepare(stacked, ctx.positions, slots, plane, wn[:rank].contiguous(), freq, 1e-6, H, hd, rot, rank))
+        hbm(f"latent_prepare_{label}", us, n * (H * rot * 4 + (rank + rot) * 4), like="llama_rope_kv_write")
+        table_r = torch.randn(4096, 64, device=device)
+        us = timed(lambda: ops.rope_kv_write(tq, ctx.positions, table_r, slots, tpool, tH, tKV, 64))
+        hbm(f"llama_rope_kv_write_{label}", us, n * ((tH + tKV) * 64 * 4 + tKV * 64 * 4))
+        up = torch.randn(n, ff, device=device).to(bf)
+        us = timed(lambda: ops.unary(up, "relu2"))
+        hbm(f"relu2_{label}", us, n * ff * 4, like="llama_swiglu")
+        gu = torch.randn(n, 2 * twin["intermediate_size"], device=device).to(bf)
+        us = timed(lambda: ops.swiglu(gu))
+        hbm(f"llama_swiglu_{label}", us, n * twin["intermediate_size"] * 6)
+    out["kernels"] = kernels
+    out["peaks"] = {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"]}
+    print(json.dumps(out, indent=1))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -202,6 +392,9 @@ def main() -> int:
                          "fixed number of pages, with preemption")
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (recorded in config)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64, the end-to-end run and the kernel table")
+    ap.add_argument("--design", choices=["nurolorn-small", "nurolorn-1b"], default=None,
+                    help="instead of the one line: prefill and decode throughput of a Nurolorn configuration beside a Llama of "
+                         "equal width, depth and feed-forward size, and the design's own kernels against their rooflines")
     ap.add_argument("--sweep", action="store_true",
                     help="instead of the one line: a table of decode steps over batch sizes and context lengths and of prefills over prompt lengths")
     args = ap.parse_args()
@@ -212,6 +405,8 @@ def main() -> int:
         args.warmup = 3
     if args.impl == "reference":
         return reference_arm(args)
+    if args.design:
+        return design_comparison(args)
 
     import random
 

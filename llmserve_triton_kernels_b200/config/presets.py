@@ -21,7 +21,27 @@ def _llama(**kw) -> dict:
     return base
 
 
+def _nurolorn(width: int, ff: int, heads: int, rank: int, rot: int, window: int, pattern: str, loop, vocab: int = 32000) -> dict:
+    """``pattern``: one letter a layer, L latent attention, G minGRU, W window attention; every layer has a dense feed-forward."""
+    head = 64
+    kinds = {
+        "L": lambda: {"type": "latent_attention", "mixer": {"heads": heads, "dim": head, "rot_dim": rot, "vdim": head, "kv_rank": rank,
+                                                            "scale": (head + rot) ** -0.5, "rot": {"base": 10000.0, "dims": rot}}},
+        "G": lambda: {"type": "mingru", "mixer": {"width": width}},
+        "W": lambda: {"type": "attention", "mixer": {"heads": heads, "kv_heads": max(1, heads // 8), "dim": head, "vdim": head,
+                                                     "scale": head ** -0.5, "mask": {"size": window}}},
+    }
+    layers = [{**kinds[c](), "mlp": {"kind": "dense", "ff": ff}} for c in pattern]
+    return {
+        "architecture": "Nurolorn", "vocab": vocab, "width": width, "layers": layers, "norm": {"eps": 1e-6, "groups": 2},
+        "residual_mult": 0.7, "logit_scale": 1.0, "loop": dict(zip(("start", "stop", "times"), loop)),
+    }
+
+
 PRESETS: dict[str, dict] = {
+    # Nurolorn at sizes that resemble real layers (the design has no published sizes): a stretch of four layers runs twice
+    "nurolorn-small": _nurolorn(1024, 4096, 16, 128, 32, 512, "LLGWLL", (1, 5, 2)),
+    "nurolorn-1b": _nurolorn(2048, 8192, 32, 256, 32, 1024, "LLGWLLGWLL", (2, 8, 2)),
     "tiny": _llama(
         vocab_size=256, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
         num_key_value_heads=2, max_position_embeddings=512,

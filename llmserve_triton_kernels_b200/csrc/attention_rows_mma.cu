@@ -74,25 +74,25 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
 
     const int* table = a.page_table + (size_t)r * a.table_width;
     const int k_chunks = dk >> 3, v_chunks = dv >> 3;
+    pdl_trigger();
+    pdl_wait();  // the queries and the newest cached rows are the work of the kernels in front
+    // eight lanes a key (128 bytes of its row a pass), sixteen keys a pass of the CTA: a key's page is looked up once
     auto load_tile = [&](int t, int stage) {
-        const int j0 = j_first + t * BN;
+        const int j0 = j_first + t * BN, sub = tid & 7;
         bf16* kd = Ks + stage * BN * kp;
-        for (int i = tid; i < BN * k_chunks; i += THREADS) {
-            const int key = i / k_chunks, c = i - key * k_chunks, j = j0 + key;
+        bf16* vd = Vs + stage * BN * vp;
+        for (int key = tid >> 3; key < BN; key += THREADS / 8) {
+            const int j = j0 + key;
             const bool valid = j < ctx_len;
-            const bf16* src = a.keys;
-            if (valid) src += (long long)table[j / a.page_size] * a.k_page + (long long)kvh * a.k_head + (long long)(j % a.page_size) * a.k_token + c * 8;
-            cp_async16(kd + key * kp + c * 8, src, valid);
-        }
-        if (!alias) {
-            bf16* vd = Vs + stage * BN * vp;
-            for (int i = tid; i < BN * v_chunks; i += THREADS) {
-                const int key = i / v_chunks, c = i - key * v_chunks, j = j0 + key;
-                const bool valid = j < ctx_len;
-                const bf16* src = a.values;
-                if (valid) src += (long long)table[j / a.page_size] * a.v_page + (long long)kvh * a.v_head + (long long)(j % a.page_size) * a.v_token + c * 8;
-                cp_async16(vd + key * vp + c * 8, src, valid);
+            long long k_off = 0, v_off = 0;
+            if (valid) {
+                const int page = table[j / a.page_size], off = j % a.page_size;
+                k_off = (long long)page * a.k_page + (long long)kvh * a.k_head + (long long)off * a.k_token;
+                v_off = (long long)page * a.v_page + (long long)kvh * a.v_head + (long long)off * a.v_token;
             }
+            for (int c = sub; c < k_chunks; c += 8) cp_async16(kd + key * kp + c * 8, a.keys + k_off + c * 8, valid);
+            if (!alias)
+                for (int c = sub; c < v_chunks; c += 8) cp_async16(vd + key * vp + c * 8, a.values + v_off + c * 8, valid);
         }
     };
 
@@ -139,6 +139,7 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
         float s[BN / 8][4];
 #pragma unroll
         for (int i = 0; i < BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll 2
         for (int ks = 0; ks < dk; ks += 16) {
             unsigned qa[4];
             ldmatrix_x4(qa, Qs + (warp * 16 + (lane & 15)) * kp + ks + (lane >> 4) * 8);
@@ -250,6 +251,8 @@ attention_rows_merge_kernel(const float* __restrict__ part_o, const float* __res
                             long long out_token, long long out_head, int n_tokens, int H, int dv, int splits) {
     const int lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    pdl_trigger();
+    pdl_wait();
     if (item >= (long long)n_tokens * H) return;
     const int t = (int)(item / H), h = (int)(item - (long long)t * H);
     const float* ml = part_ml + (size_t)item * splits * 2;
@@ -278,8 +281,7 @@ int launch(const RowsArgs<bf16>& a, int requests, int max_query_len, int splits,
     const int group = a.H / a.KV;
     const long long tiles = ((long long)max_query_len * group + BM - 1) / BM;
     if (tiles * splits > 0x7fffffffLL || a.KV > 65535 || requests > 65535) return LLM_ERR_UNSUPPORTED;
-    kernel<<<dim3((unsigned)(tiles * splits), a.KV, requests), THREADS, smem, stream>>>(a, splits, part_o, part_ml);
-    return launch_status();
+    return launch_pdl(kernel, dim3((unsigned)(tiles * splits), a.KV, requests), dim3(THREADS), smem, stream, a, splits, part_o, part_ml);
 }
 
 }  // namespace
@@ -336,7 +338,6 @@ LLM_EXPORT int llm_attention_rows_mma(const void* q0, long long q0_token, long l
                     : launch<256, 32>(a, requests, max_query_len, splits, part_o, part_ml, smem, stream);
     if (code != 0 || splits == 1) return code;
     const long long items = (long long)n_tokens * H;
-    attention_rows_merge_kernel<<<(unsigned)((items + 3) / 4), 128, 0, stream>>>(part_o, part_ml, (bf16*)out, out_token, out_head,
-                                                                                n_tokens, H, dv, splits);
-    return launch_status();
+    return launch_pdl(attention_rows_merge_kernel, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, (const float*)part_o,
+                      (const float*)part_ml, (bf16*)out, out_token, out_head, n_tokens, H, dv, splits);
 }

@@ -299,14 +299,16 @@ LLM_EXPORT int llm_linear_decode_parts(int N) { return (N + 15) / 16; }
 //   mode 1: w = [gate | up] with the up rows starting at row up_offset; out [M, N] = silu(gate) * up.
 //   mode 2: resid [M, N] += product; xw_out [M, N] = resid * norm_w; ss_out [parts(N), M] = partial sums
 //           of resid^2.  out is not used.
+//   mode 4: mode 0 with the square of relu on the product.
+//   mode 5: resid [M, N] += resid_scale * product and nothing else (norm_w, xw_out, ss_out are not used).
 // in_ss (or null): [in_parts, M] partial sums of squares; the product is scaled by
 // rsqrt(sum / K + in_eps) per row.  Needs M <= 16, K a multiple of 64 (the weights travel in pieces of 64 k), 16-byte aligned rows;
 // otherwise it returns LLM_ERR_UNSUPPORTED and the caller takes another route.  error_flag (host-visible
 // int, or null) is set to 1 if a bounded wait inside the kernel ever gives up.
 LLM_EXPORT int llm_linear_decode(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int ldx,
                                  int ldo, const float* in_ss, int in_parts, float in_eps, int mode, int up_offset,
-                                 float* resid, const float* norm_w, void* xw_out, float* ss_out, int* error_flag,
-                                 cudaStream_t stream) {
+                                 float* resid, const float* norm_w, void* xw_out, float* ss_out, float resid_scale,
+                                 int* error_flag, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 16 || K < 64 || (K & 63) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return LLM_ERR_UNSUPPORTED;
     LinearParams p = {};
@@ -326,7 +328,20 @@ LLM_EXPORT int llm_linear_decode(const void* x, const void* w, void* out, int ou
     p.norm_w = norm_w;
     p.xw_out = (__nv_bfloat16*)xw_out;
     p.ss_out = ss_out;
+    p.resid_scale = 1.f;
     p.error_flag = error_flag;
+    if (mode == 5) {  // the scaled sum alone
+        if (!resid) return LLM_ERR_BAD_ARGUMENT;
+        p.norm_w = nullptr;
+        p.xw_out = nullptr;
+        p.ss_out = nullptr;
+        p.resid_scale = resid_scale;
+        return dispatch<MODE_RESIDUAL, __nv_bfloat16>(p, stream);
+    }
+    if (mode == 4) {
+        p.act = 1;
+        mode = MODE_PLAIN;
+    }
     if (mode == MODE_RESIDUAL) {
         if (!resid || !norm_w || !xw_out || !ss_out) return LLM_ERR_BAD_ARGUMENT;
         return dispatch<MODE_RESIDUAL, __nv_bfloat16>(p, stream);

@@ -45,6 +45,8 @@ struct LinearParams {
     const float* norm_w;    // MODE_RESIDUAL: [N] weight of the next norm
     __nv_bfloat16* xw_out;  // MODE_RESIDUAL: [M, N] = resid * norm_w
     float* ss_out;          // MODE_RESIDUAL: [tiles of 16 features, M]
+    float resid_scale;      // MODE_RESIDUAL: the product enters the stream times this
+    int act;                // MODE_PLAIN: 0 the product as it is, 1 the square of its relu
     int* error_flag;        // set to 1 if a wait for a copy gave up (host-visible memory), or null
     int group;              // warps that share a tile: 1, 2, 4 or 8
     int slots;              // boxes of a warp's ring: 2 to SLOTS
@@ -208,7 +210,7 @@ __device__ __forceinline__ void stream_plan(StreamState& st, const LinearParams&
         } else if constexpr (MODE == MODE_RESIDUAL) {
             const int n0 = tile * 16;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) st.e_norm[h] = n0 + qr + 8 * h < p.N ? p.norm_w[n0 + qr + 8 * h] : 0.f;
+            for (int h = 0; h < 2; ++h) st.e_norm[h] = p.norm_w && n0 + qr + 8 * h < p.N ? p.norm_w[n0 + qr + 8 * h] : 0.f;
             st.early = true;
         }
     }
@@ -439,13 +441,22 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                     if (live) {
                         const bool have = ti == 0 && st.early;
                         const float before = ti == 0 && st.have_resid ? st.e_resid[t][e] : p.resid[(size_t)m * N + n];
-                        const float v = before + s;
+                        const float v = fmaf(p.resid_scale, s, before);
                         p.resid[(size_t)m * N + n] = v;
-                        p.xw_out[(size_t)m * N + n] = __float2bfloat16_rn(v * (have ? st.e_norm[e >> 1] : p.norm_w[n]));
-                        sq[e & 1] += v * v;
+                        if (p.norm_w) {  // null: the sum alone, no hand-over to a norm
+                            p.xw_out[(size_t)m * N + n] = __float2bfloat16_rn(v * (have ? st.e_norm[e >> 1] : p.norm_w[n]));
+                            sq[e & 1] += v * v;
+                        }
                     }
                 } else {
-                    if (live) reinterpret_cast<TO*>(p.out)[(size_t)m * p.ldo + n] = from_float<TO>(s);
+                    if (live) {
+                        float r = s;
+                        if (p.act == 1) {
+                            r = fmaxf(r, 0.f);
+                            r *= r;
+                        }
+                        reinterpret_cast<TO*>(p.out)[(size_t)m * p.ldo + n] = from_float<TO>(r);
+                    }
                 }
             }
             if constexpr (MODE == MODE_RESIDUAL) {
@@ -457,7 +468,7 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                     v += __shfl_xor_sync(0xffffffffu, v, 8);
                     v += __shfl_xor_sync(0xffffffffu, v, 16);
                     const int m = 8 * t + 2 * qc + j;
-                    if (qr == 0 && m < M) p.ss_out[(size_t)tile * M + m] = v;
+                    if (qr == 0 && m < M && p.ss_out) p.ss_out[(size_t)tile * M + m] = v;
                 }
             }
         }

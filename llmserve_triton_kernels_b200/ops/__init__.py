@@ -32,7 +32,7 @@ _SIGNATURES = {
     "llm_check_step_arrays": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "llm_check_page_group": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "llm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
-    "llm_linear_decode": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
+    "llm_linear_decode": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _f, _vp, _vp],
     "llm_linear_decode_qkv": [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _f, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "llm_gemm_tcgen05": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "llm_gemm_tcgen05_fused": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp],
@@ -46,7 +46,7 @@ _SIGNATURES = {
     "llm_stream_inject": [_vp, _vp, _i, _f, _vp, _vp, _i, _i, _vp, _i, _i, _vp],
     "llm_unary": [_vp, _i, _vp, _i, _i, _i, _i, _i, _f, _vp],
     "llm_gate_mul": [_vp, _ll, _ll, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
-    "llm_mingru_scan": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "llm_mingru_scan": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "llm_latent_prepare": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _vp],
     "llm_unit_norm_kv_write": [_vp, _i, _i, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "llm_attention_rows": [_vp, _ll, _ll, _i, _vp, _ll, _ll, _i, _vp, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _i, _i,
@@ -361,12 +361,22 @@ class ResidualSink:
             ss = torch.empty((parts, m), dtype=torch.float32, device=x.device)
             code = _launch(
                 "llm_linear_decode", _ptr(x), _ptr(w), None, _BF16, m, n, k, x.stride(0), n, None, 0, 0.0, 2, 0,
-                _ptr(self.resid), _ptr(self.weight), _ptr(xw), _ptr(ss), _error_flag_ptr(), _stream(),
+                _ptr(self.resid), _ptr(self.weight), _ptr(xw), _ptr(ss), 1.0, _error_flag_ptr(), _stream(),
             )
             if code != 10002:
                 _check(code, "linear into the residual stream")
                 return NormedInput(xw, ss, self.eps, self.norm)
             add_launches(-1)  # a shape the kernel refuses: the library's way below
+        elif m <= _DECODE_LINEAR_MAX_ROWS:
+            # the same kernel adds its product, times alpha, into the stream and leaves the norm to its own kernel
+            code = _launch(
+                "llm_linear_decode", _ptr(x), _ptr(w), None, _BF16, m, n, k, x.stride(0), n, None, 0, 0.0, 5, 0,
+                _ptr(self.resid), None, None, None, self.alpha, _error_flag_ptr(), _stream(),
+            )
+            if code != 10002:
+                _check(code, "linear into the residual stream (scaled)")
+                return ADDED
+            add_launches(-1)
         if _GEMM_POLICY == "own" and m >= _TCGEN05_MIN_ROWS:
             return None  # the caller runs the own tcgen05 product and leaves the sum to the norm's kernel
         library()
@@ -407,7 +417,7 @@ def _decode_linear(x, w, out_dtype, mode: int, n_out: int, up_offset: int = 0):
     code = _launch(
         "llm_linear_decode", _ptr(xt), _ptr(w), _ptr(out), _code(out_dtype), m, n_out, k, xt.stride(0), n_out,
         _ptr(x.ss) if scaled else None, x.ss.shape[0] if scaled else 0, x.eps if scaled else 0.0, mode, up_offset,
-        None, None, None, None, _error_flag_ptr(), _stream(),
+        None, None, None, None, 1.0, _error_flag_ptr(), _stream(),
     )
     if code == 10002:  # a shape the kernel refuses
         add_launches(-1)
@@ -869,7 +879,12 @@ def unary(x: torch.Tensor, kind: str, alpha: float = 1.0, inplace: bool = False)
 
 def linear_act(x, w: torch.Tensor, activation: str) -> torch.Tensor:
     """``act(x @ w^T)`` for a one-input activation (see :func:`unary`): the product, then the activation on its
-    result in place."""
+    result in place; for few bfloat16 rows the square of relu is the end of the weight-streaming product itself."""
+    xt = x.xw if isinstance(x, NormedInput) else x
+    if activation == "relu2" and xt.dtype == torch.bfloat16 and xt.shape[0] <= _DECODE_LINEAR_MAX_ROWS:
+        out = _decode_linear(x, w, torch.bfloat16, 4, w.shape[0])
+        if out is not None:
+            return out
     return unary(linear(x, w), activation, inplace=True)
 
 
@@ -888,10 +903,11 @@ def gate_mul(a: torch.Tensor, b: torch.Tensor, kind: str = "sigmoid") -> torch.T
 
 
 def mingru_scan(proj: torch.Tensor, bias_z, bias_u, states: torch.Tensor, state_slots: torch.Tensor, cu_tokens: torch.Tensor,
-                num_requests: int, width: int, out_dtype: torch.dtype) -> torch.Tensor:
+                num_requests: int, width: int, out_dtype: torch.dtype, max_query_len: int = 1 << 30) -> torch.Tensor:
     """The minGRU recurrence over a flat batch.  ``proj [N, 3 * width]`` holds the pre-activations of the update
     gate, the candidate and the output gate; ``states [slots, width]`` (float32) is read at ``state_slots[r]`` for
-    request r, walked over the request's tokens ``cu_tokens[r]:cu_tokens[r+1]`` and written back.  Returns
+    request r, walked over the request's tokens ``cu_tokens[r]:cu_tokens[r+1]`` and written back.  ``max_query_len``:
+    the most tokens a request brings (long requests are shared out over the warps of a CTA).  Returns
     ``state_t * silu(output gate)`` ``[N, width]`` in ``out_dtype``."""
     _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] >= 3 * width, "mingru_scan: proj rows hold three pre-activations")
     _need(states.dtype == torch.float32 and states.is_contiguous() and states.shape[1] == width, "mingru_scan: states must be float32 [slots, width]")
@@ -901,7 +917,7 @@ def mingru_scan(proj: torch.Tensor, bias_z, bias_u, states: torch.Tensor, state_
     _i32(cu_tokens, "cu_tokens")
     out = torch.empty((proj.shape[0], width), dtype=out_dtype, device=proj.device)
     code = _launch("llm_mingru_scan", _ptr(proj), _code(proj.dtype), proj.stride(0), _ptr(bias_z), _ptr(bias_u), _ptr(states),
-                   _ptr(state_slots), _ptr(cu_tokens), _ptr(out), _code(out_dtype), width, int(num_requests), width, _stream())
+                   _ptr(state_slots), _ptr(cu_tokens), _ptr(out), _code(out_dtype), width, int(num_requests), width, int(max_query_len), _stream())
     _check(code, "mingru_scan")
     return out
 

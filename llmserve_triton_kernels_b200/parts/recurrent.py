@@ -52,7 +52,7 @@ class MinGRU(Mixer):
 
     def forward(self, x, ctx, cache, sink=None):
         proj = ops.linear(x, self.w_in, out_dtype=torch.float32)  # [N, z | x | gate], 32-bit
-        out = ops.mingru_scan(proj, self.b_z, self.b_x, cache.states, cache.slots, ctx.cu_tokens, ctx.num_requests, self.width, self.dtype)
+        out = ops.mingru_scan(proj, self.b_z, self.b_x, cache.states, cache.slots, ctx.cu_tokens, ctx.num_requests, self.width, self.dtype, ctx.max_query_len)
         if sink is not None:
             handed_on = sink.linear(out, self.w_out)
             if handed_on is not None:

@@ -181,7 +181,7 @@ def gate_mul(a, b, kind="sigmoid"):
     return (a.float().reshape(n, heads * w) * g).to(a.dtype)
 
 
-def mingru_scan(proj, bias_z, bias_u, states, state_slots, cu_tokens, num_requests, width, out_dtype):
+def mingru_scan(proj, bias_z, bias_u, states, state_slots, cu_tokens, num_requests, width, out_dtype, max_query_len=None):
     out = torch.empty((proj.shape[0], width), dtype=out_dtype, device=proj.device)
     p = proj.float()
     cu = cu_tokens.tolist()

@@ -110,17 +110,19 @@ def test_head_linear(ops, dtype):
     close(ops.head_linear(x, w), plain_ops.head_linear(x, w), dtype, "one product per head")
 
 
+@pytest.mark.parametrize("lens", [[1, 13, 2, 30], [1, 200, 65, 3], [777, 1, 1, 1]])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-def test_mingru_scan_carries_the_state_of_each_slot(ops, out_dtype):
-    width, lens = 45, [1, 13, 2, 30]
-    ctx, _, _ = make_ctx(lens, lens, 4, 40)
+def test_mingru_scan_carries_the_state_of_each_slot(ops, out_dtype, lens):
+    """Short requests (a thread walks a channel) and long ones (the warps of a CTA share a request's tokens)."""
+    width = 45
+    ctx, _, _ = make_ctx(lens, lens, 4, 400)
     slots = torch.tensor([2, 0, 5, 3], dtype=torch.int32, device=DEV)
     bz, bu = rnd(width, seed=1), rnd(width, seed=2)
     states = rnd(7, width, seed=3)
     for step in range(2):  # the second step goes on from the states the first one left
         proj = rnd(sum(lens), 3 * width + 2, seed=10 + step, scale=1.5)[:, : 3 * width]
         a, b = states.clone(), states.clone()
-        got = ops.mingru_scan(proj, bz, bu, a, slots, ctx.cu_tokens, 4, width, out_dtype)
+        got = ops.mingru_scan(proj, bz, bu, a, slots, ctx.cu_tokens, 4, width, out_dtype, max(lens))
         want = plain_ops.mingru_scan(proj, bz, bu, b, slots, ctx.cu_tokens, 4, width, out_dtype)
         close(got, want, out_dtype, "outputs")
         close(a, b, torch.float32, "states")
