@@ -126,6 +126,7 @@ LLM_EXPORT int llm_attention_rows(const void* q0, long long q0_token, long long 
         a.slopes = slopes;
         a.table_width = table_width; a.n_tokens = n_tokens; a.H = H; a.KV = KV; a.page_size = page_size; a.window = window;
         a.scale = scale;
+        a.key_part = 0; a.keys1 = nullptr; a.k1_token = 0; a.fresh_d0 = 0; a.stats = nullptr;
     };
     if (dtype == LLM_F32) {
         RowsArgs<float> a;

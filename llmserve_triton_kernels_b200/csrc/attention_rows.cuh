@@ -21,5 +21,16 @@ struct RowsArgs {
     const float* slopes;  // per query head: the score of key j for the query at position i loses slope * (i - j); null: none
     int table_width, n_tokens, H, KV, page_size, window;
     float scale;
+    // Which keys: 0 all that a row sees; 1 only those cached before this step (positions before the request's first new
+    // token); 2 only the step's own tokens, whose keys and values then lie token by token, not in pages: token i of the
+    // flat batch at keys + i * k_token + head * k_head (lanes [0, fresh_d0)) and at keys1 + i * k1_token (the lanes
+    // behind them, shared by all heads; null: all lanes at keys), its value at values + i * v_token + head * v_head.
+    int key_part;
+    const T* keys1;
+    long long k1_token;
+    int fresh_d0;
+    // [n_tokens, H, 2] (or null): the row's maximum score (times log2 e) and the sum of its exponentials, for a merge of two parts; a
+    // row that saw no key says (-inf, 0) and its output is not to be read
+    float* stats;
 };
 

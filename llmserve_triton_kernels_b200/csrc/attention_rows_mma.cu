@@ -15,7 +15,7 @@
 namespace {
 
 using bf16 = __nv_bfloat16;
-constexpr int BM = 64, WARPS = 4, THREADS = WARPS * 32, PAD = 8;
+constexpr int PAD = 8;
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const bf16* p) {
@@ -44,19 +44,24 @@ __device__ __forceinline__ unsigned pack2(float lo, float hi) {
     return *reinterpret_cast<const unsigned*>(&v);
 }
 
-template <int DV_MAX, int BN>
-__global__ void __launch_bounds__(THREADS)
+// BM rows a CTA (64 or 128: sixteen a warp).  The larger tile halves the trips of keys and values from L2 per row, which
+// is what bounds requests that bring many rows per key/value head.
+template <int DV_MAX, int BN, int BM>
+__global__ void __launch_bounds__(BM * 2, (DV_MAX <= 64 ? 4 : (DV_MAX <= 128 ? 3 : 2)) * 64 / BM)
 attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
+    constexpr int THREADS = BM * 2;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int dk = a.d0 + a.d1, dv = a.dv, kp = dk + PAD, vp = dv + PAD;
-    const bool alias = a.values == a.keys && a.v_page == a.k_page && a.v_head == a.k_head && a.v_token == a.k_token;
+    const bool alias = a.key_part != 2 && a.values == a.keys && a.v_page == a.k_page && a.v_head == a.k_head && a.v_token == a.k_token;
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);  // [BM][kp]
     bf16* Ks = Qs + BM * kp;                       // [2][BN][kp]
     bf16* Vs = alias ? Ks : Ks + 2 * BN * kp;      // [2][BN][vp] unless the values are the head of the key rows
     const int v_pitch = alias ? kp : vp, v_stage = alias ? BN * kp : BN * vp;
 
     const int r = blockIdx.z, kvh = blockIdx.y;
-    const int tile = blockIdx.x / splits, split = blockIdx.x - tile * splits;
+    // the last row tiles of a request see the most keys: they are handed out first, so that no long CTA starts last
+    const int slot = blockIdx.x / splits, split = blockIdx.x - slot * splits;
+    const int tile = (int)(gridDim.x / splits) - 1 - slot;
     const int group = a.H / a.KV;
     const int q_begin = a.cu_tokens[r], q_len = a.cu_tokens[r + 1] - q_begin, ctx_len = a.ctx_lens[r];
     const int rows_total = q_len * group, row0 = tile * BM;
@@ -66,12 +71,24 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
 
     // the keys this tile's rows see, and this split's share of their tiles
     const int pos_min = first_pos + row0 / group, pos_max = first_pos + min(rows_total - 1, row0 + BM - 1) / group;
-    const int key_lo = a.window > 0 ? max(0, pos_min - a.window + 1) : 0;
+    int key_lo = a.window > 0 ? max(0, pos_min - a.window + 1) : 0, key_hi = pos_max;
+    if (a.key_part == 1) key_hi = min(key_hi, first_pos - 1);  // only what was cached before this step
+    if (a.key_part == 2) key_lo = max(key_lo, first_pos);     // only the step's own tokens
     const int j_first = (key_lo / BN) * BN;
-    const int n_tiles = (pos_max - j_first) / BN + 1;
+    const int n_tiles = key_hi >= j_first ? (key_hi - j_first) / BN + 1 : 0;
     const int per = (n_tiles + splits - 1) / splits;
     const int t_begin = split * per, t_end = min(n_tiles, t_begin + per);
 
+    if (n_tiles == 0 && splits == 1 && a.stats) {  // a part without keys for these rows: statistics that say so, and
+        for (int i = tid; i < BM; i += THREADS) {     // an output that the merge does not read
+            const int R = row0 + i;
+            if (R >= rows_total) break;
+            const int t = q_begin + R / group, h = kvh * group + R % group;
+            a.stats[((size_t)t * a.H + h) * 2] = -INFINITY;
+            a.stats[((size_t)t * a.H + h) * 2 + 1] = 0.f;
+        }
+        return;
+    }
     const int* table = a.page_table + (size_t)r * a.table_width;
     const int k_chunks = dk >> 3, v_chunks = dv >> 3;
     pdl_trigger();
@@ -83,6 +100,17 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
         bf16* vd = Vs + stage * BN * vp;
         for (int key = tid >> 3; key < BN; key += THREADS / 8) {
             const int j = j0 + key;
+            if (a.key_part == 2) {  // the step's own tokens, token by token
+                const bool valid = j >= first_pos && j < ctx_len;
+                const long long i = valid ? q_begin + (j - first_pos) : 0;
+                const bf16* k0 = a.keys + i * a.k_token + (long long)kvh * a.k_head;
+                const bf16* k1 = a.keys1 ? a.keys1 + i * a.k1_token : k0;
+                const int c0 = a.keys1 ? a.fresh_d0 >> 3 : k_chunks;
+                for (int c = sub; c < k_chunks; c += 8) cp_async16(kd + key * kp + c * 8, c < c0 ? k0 + c * 8 : k1 + (c - c0) * 8, valid);
+                const bf16* v0 = a.values + i * a.v_token + (long long)kvh * a.v_head;
+                for (int c = sub; c < v_chunks; c += 8) cp_async16(vd + key * vp + c * 8, v0 + c * 8, valid);
+                continue;
+            }
             const bool valid = j < ctx_len;
             long long k_off = 0, v_off = 0;
             if (valid) {
@@ -112,14 +140,26 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
     cp_async_commit();
 
     // the two rows of this thread: (lane / 4) and (lane / 4 + 8) of the warp's sixteen
-    int pos[2], lo[2];
+    int pos[2], lo[2], hi[2];
     float slope[2];
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
         const int R = min(row0 + warp * 16 + (lane >> 2) + 8 * e, rows_total - 1);
         pos[e] = first_pos + R / group;
         lo[e] = a.window > 0 ? max(0, pos[e] - a.window + 1) : 0;
-        slope[e] = a.slopes ? a.slopes[kvh * group + R % group] : 0.f;
+        if (a.key_part == 2) lo[e] = max(lo[e], first_pos);
+        hi[e] = a.key_part == 1 ? min(pos[e], first_pos - 1) : pos[e];
+        slope[e] = a.slopes ? a.slopes[kvh * group + R % group] * LOG2E : 0.f;
+    }
+    const float scale2 = a.scale * LOG2E;
+    // the keys that every row of this warp sees: from the newest row's window start to the oldest row's position
+    int warp_lo, warp_hi;
+    {
+        const int R0 = min(row0 + warp * 16, rows_total - 1), R1 = min(row0 + warp * 16 + 15, rows_total - 1);
+        const int p0 = first_pos + R0 / group, p1 = first_pos + R1 / group;
+        warp_lo = a.window > 0 ? max(0, p1 - a.window + 1) : 0;
+        if (a.key_part == 2) warp_lo = max(warp_lo, first_pos);
+        warp_hi = a.key_part == 1 ? min(p0, first_pos - 1) : p0;
     }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float o[DV_MAX / 8][4];
@@ -151,15 +191,16 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
                 mma_bf16(s[nb + 1], qa, kb[2], kb[3]);
             }
         }
-        // scale, bias, mask; the tile's maximum per row
+        // scale, bias, mask (scores in units of log 2 from here on); the tile's maximum per row
         float tile_max[2] = {-INFINITY, -INFINITY};
+        const bool whole = j0 >= warp_lo && j0 + BN - 1 <= warp_hi;  // every row of the warp sees every key of the tile
 #pragma unroll
         for (int nb = 0; nb < BN / 8; ++nb)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int e = c >> 1, j = j0 + nb * 8 + (lane & 3) * 2 + (c & 1);
-                float v = s[nb][c] * a.scale - slope[e] * (float)(pos[e] - j);
-                v = (j >= lo[e] && j <= pos[e]) ? v : -INFINITY;
+                float v = fmaf(s[nb][c], scale2, -slope[e] * (float)(pos[e] - j));
+                if (!whole) v = (j >= lo[e] && j <= hi[e]) ? v : -INFINITY;
                 s[nb][c] = v;
                 tile_max[e] = fmaxf(tile_max[e], v);
             }
@@ -170,7 +211,7 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
             tile_max[e] = fmaxf(tile_max[e], __shfl_xor_sync(0xffffffffu, tile_max[e], 2));
             const float m_new = fmaxf(m[e], tile_max[e]);
             m_use[e] = m_new == -INFINITY ? 0.f : m_new;  // a row that has seen no key yet
-            rescale[e] = exp2f((m[e] - m_use[e]) * LOG2E);
+            rescale[e] = exp2f(m[e] - m_use[e]);
             m[e] = m_new;
             l[e] *= rescale[e];
         }
@@ -184,7 +225,7 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
         for (int nb = 0; nb < BN / 8; ++nb)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const float p = exp2f((s[nb][c] - m_use[c >> 1]) * LOG2E);
+                const float p = exp2f(s[nb][c] - m_use[c >> 1]);
                 s[nb][c] = p;
                 l[c >> 1] += p;
             }
@@ -220,7 +261,11 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
         if (R >= rows_total) continue;
         const int t = q_begin + R / group, h = kvh * group + R % group;
         if (splits == 1) {
-            const float inv = 1.f / l[e];
+            const float inv = l[e] > 0.f ? 1.f / l[e] : 0.f;  // no key seen (a part without keys for this row): zeros
+            if (a.stats && (lane & 3) == 0) {
+                a.stats[((size_t)t * a.H + h) * 2] = m[e];  // in units of log 2, as the merge expects
+                a.stats[((size_t)t * a.H + h) * 2 + 1] = l[e];
+            }
             bf16* op = a.out + (long long)t * a.out_token + (long long)h * a.out_head;
 #pragma unroll
             for (int i = 0; i < DV_MAX / 8; ++i)
@@ -256,24 +301,63 @@ attention_rows_merge_kernel(const float* __restrict__ part_o, const float* __res
     if (item >= (long long)n_tokens * H) return;
     const int t = (int)(item / H), h = (int)(item - (long long)t * H);
     const float* ml = part_ml + (size_t)item * splits * 2;
-    float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, ml[2 * s]);
-    float L = 0.f;
-    for (int s = 0; s < splits; ++s) L += ml[2 * s] == -INFINITY ? 0.f : exp2f((ml[2 * s] - M) * LOG2E) * ml[2 * s + 1];
-    const float inv = 1.f / L;
+    // lane s holds the weight of split s (at most 32 splits): exp(m_s - M), and the sum of all of them times their sums
+    const float ms = lane < splits ? ml[2 * lane] : -INFINITY, ls = lane < splits ? ml[2 * lane + 1] : 0.f;
+    const float M = warp_max(ms);
+    const float ws = ms == -INFINITY ? 0.f : exp2f(ms - M);  // the kernel's maxima are in units of log 2
+    const float inv = 1.f / warp_sum(ws * ls);
     bf16* op = out + (long long)t * out_token + (long long)h * out_head;
-    for (int d = lane; d < dv; d += 32) {
-        float acc = 0.f;
-        for (int s = 0; s < splits; ++s)
-            if (ml[2 * s] != -INFINITY) acc += exp2f((ml[2 * s] - M) * LOG2E) * part_o[((size_t)item * splits + s) * dv + d];
-        op[d] = __float2bfloat16_rn(acc * inv);
+    const float* po = part_o + (size_t)item * splits * dv;
+    for (int d0 = 0; d0 < dv; d0 += 256) {  // eight independent sums a lane, so that a split's loads are in flight together
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int s = 0; s < splits; ++s) {
+            const float w = __shfl_sync(0xffffffffu, ws, s);
+            if (w == 0.f) continue;  // uniform across the warp
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int d = d0 + lane + 32 * i;
+                if (d < dv) acc[i] = fmaf(w, po[(size_t)s * dv + d], acc[i]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int d = d0 + lane + 32 * i;
+            if (d < dv) op[d] = __float2bfloat16_rn(acc[i] * inv);
+        }
     }
 }
 
-template <int DV_MAX, int BN>
+// out[t, h] = (w1 o1 + w2 o2) / (w1 + w2) with w = sum * 2^(maximum - M): two parts of one softmax, each normalised by
+// itself, joined.  o1, o2 [n, H, dv] with token and head strides; one warp per (token, head).
+__global__ void __launch_bounds__(128)
+merge_two_parts_kernel(const bf16* __restrict__ o1, long long o1_token, long long o1_head, const float* __restrict__ stats1,
+                       const bf16* __restrict__ o2, long long o2_token, long long o2_head, const float* __restrict__ stats2,
+                       bf16* __restrict__ out, long long out_token, long long out_head, int n_tokens, int H, int dv) {
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    pdl_trigger();
+    pdl_wait();
+    if (item >= (long long)n_tokens * H) return;
+    const int t = (int)(item / H), h = (int)(item - (long long)t * H);
+    const float m1 = stats1[item * 2], l1 = stats1[item * 2 + 1], m2 = stats2[item * 2], l2 = stats2[item * 2 + 1];
+    const float M = fmaxf(m1, m2);
+    const float w1 = l1 > 0.f ? l1 * exp2f(m1 - M) : 0.f, w2 = l2 > 0.f ? l2 * exp2f(m2 - M) : 0.f;  // maxima in units of log 2
+    const float inv = 1.f / (w1 + w2);
+    const bf16* a = o1 + (long long)t * o1_token + (long long)h * o1_head;
+    const bf16* b = o2 + (long long)t * o2_token + (long long)h * o2_head;
+    bf16* o = out + (long long)t * out_token + (long long)h * out_head;
+    // a part without keys has weight 0 and an output that was never written: it is not read
+    for (int d = lane; d < dv; d += 32) {
+        const float av = w1 > 0.f ? __bfloat162float(a[d]) : 0.f, bv = w2 > 0.f ? __bfloat162float(b[d]) : 0.f;
+        o[d] = __float2bfloat16_rn((w1 * av + w2 * bv) * inv);
+    }
+}
+
+template <int DV_MAX, int BN, int BM = 64>
 int launch(const RowsArgs<bf16>& a, int requests, int max_query_len, int splits, float* part_o, float* part_ml, size_t smem,
            cudaStream_t stream) {
-    auto kernel = attention_rows_mma_kernel<DV_MAX, BN>;
+    constexpr int THREADS = BM * 2;
+    auto kernel = attention_rows_mma_kernel<DV_MAX, BN, BM>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -297,7 +381,8 @@ LLM_EXPORT int llm_attention_rows_mma(const void* q0, long long q0_token, long l
                                       long long v_token, int dv, const int* page_table, int table_width,
                                       const int* token_request, const int* cu_tokens, const int* ctx_lens, const float* slopes,
                                       int n_tokens, int requests, int max_query_len, int H, int KV, int page_size, int window,
-                                      float scale, int splits, float* part_o, float* part_ml, cudaStream_t stream) {
+                                      float scale, int splits, float* part_o, float* part_ml, int key_part, const void* keys1,
+                                      long long k1_token, int fresh_d0, float* stats, cudaStream_t stream) {
     if (n_tokens <= 0 || requests <= 0) return 0;
     if (d0 <= 0 || d1 < 0 || dv <= 0 || H <= 0 || KV <= 0 || H % KV || page_size <= 0 || table_width <= 0 || splits < 1 ||
         max_query_len < 1 || (d1 > 0 && q1 == nullptr) || (splits > 1 && (part_o == nullptr || part_ml == nullptr)))
@@ -305,6 +390,9 @@ LLM_EXPORT int llm_attention_rows_mma(const void* q0, long long q0_token, long l
     const int dk = d0 + d1;
     auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
     if ((d0 & 15) || (d1 & 15) || (dv & 15) || dv > 256 || dk > 640) return LLM_ERR_UNSUPPORTED;
+    if (key_part < 0 || key_part > 2 || ((key_part != 0 || stats) && splits != 1)) return LLM_ERR_BAD_ARGUMENT;
+    if (key_part == 2 && keys1 && ((fresh_d0 & 15) || fresh_d0 <= 0 || fresh_d0 >= dk || (k1_token & 7) || ((uintptr_t)keys1 & 15)))
+        return LLM_ERR_UNSUPPORTED;
     if ((q0_token & 7) || (q0_head & 7) || (q1_token & 7) || (q1_head & 7) || (k_page & 7) || (k_head & 7) || (k_token & 7) ||
         (v_page & 7) || (v_head & 7) || (v_token & 7) || (out_token & 1) || (out_head & 1))
         return LLM_ERR_UNSUPPORTED;
@@ -321,13 +409,21 @@ LLM_EXPORT int llm_attention_rows_mma(const void* q0, long long q0_token, long l
     a.slopes = slopes;
     a.table_width = table_width; a.n_tokens = n_tokens; a.H = H; a.KV = KV; a.page_size = page_size; a.window = window;
     a.scale = scale;
-    const bool alias = values == keys && v_page == k_page && v_head == k_head && v_token == k_token;
-    auto smem_for = [&](int bn) { return (size_t)(BM + 2 * bn) * (dk + PAD) * 2 + (alias ? 0 : (size_t)2 * bn * (dv + PAD) * 2); };
+    a.key_part = key_part; a.keys1 = key_part == 2 ? (const bf16*)keys1 : nullptr; a.k1_token = k1_token; a.fresh_d0 = fresh_d0;
+    a.stats = stats;
+    const bool alias = key_part != 2 && values == keys && v_page == k_page && v_head == k_head && v_token == k_token;
+    auto smem_for = [&](int bn, int bm = 64) { return (size_t)(bm + 2 * bn) * (dk + PAD) * 2 + (alias ? 0 : (size_t)2 * bn * (dv + PAD) * 2); };
     const bool wide = smem_for(64) <= 160 * 1024;
-    const size_t smem = smem_for(wide ? 64 : 32);
+    size_t smem = smem_for(wide ? 64 : 32);
     if (smem > 220 * 1024) return LLM_ERR_UNSUPPORTED;
     int code;
-    if (dv <= 64)
+    // many rows per key/value head (long prompt portions), values of at most 128 lanes: 128 rows a CTA
+    const bool tall = wide && splits == 1 && dv <= 128 && (long long)max_query_len * (H / KV) >= 512 && smem_for(64, 128) <= 100 * 1024;
+    if (tall) {
+        smem = smem_for(64, 128);
+        code = dv <= 64 ? launch<64, 64, 128>(a, requests, max_query_len, splits, part_o, part_ml, smem, stream)
+                        : launch<128, 64, 128>(a, requests, max_query_len, splits, part_o, part_ml, smem, stream);
+    } else if (dv <= 64)
         code = wide ? launch<64, 64>(a, requests, max_query_len, splits, part_o, part_ml, smem, stream)
                     : launch<64, 32>(a, requests, max_query_len, splits, part_o, part_ml, smem, stream);
     else if (dv <= 128)
@@ -340,4 +436,15 @@ LLM_EXPORT int llm_attention_rows_mma(const void* q0, long long q0_token, long l
     const long long items = (long long)n_tokens * H;
     return launch_pdl(attention_rows_merge_kernel, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, (const float*)part_o,
                       (const float*)part_ml, (bf16*)out, out_token, out_head, n_tokens, H, dv, splits);
+}
+
+// Two parts of one softmax, each normalised by itself (o [n, H, dv] bfloat16 with token and head strides, stats [n, H, 2] =
+// maximum and sum), joined into out.
+LLM_EXPORT int llm_merge_two_parts(const void* o1, long long o1_token, long long o1_head, const float* stats1, const void* o2,
+                                   long long o2_token, long long o2_head, const float* stats2, void* out, long long out_token,
+                                   long long out_head, int n_tokens, int H, int dv, cudaStream_t stream) {
+    if (n_tokens <= 0 || H <= 0 || dv <= 0) return 0;
+    const long long items = (long long)n_tokens * H;
+    return launch_pdl(merge_two_parts_kernel, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, (const bf16*)o1, o1_token,
+                      o1_head, stats1, (const bf16*)o2, o2_token, o2_head, stats2, (bf16*)out, out_token, out_head, n_tokens, H, dv);
 }

@@ -26,11 +26,13 @@ __device__ __forceinline__ void rotate_pairs(const T* __restrict__ src, T* __res
 // Latent attention.  proj row: [H x (dim | rot) queries][rank latent | rot shared key part][...].
 //   q_rot[t, h, :]   = rotate(proj query h's last rot lanes)
 //   cache[slot, :]   = [ latent / sqrt(mean(latent^2) + eps) * weight | rotate(shared key part) ]
+//   fresh[t, :]      = the same row (optional)
 // One block per token.
 template <typename T>
 __global__ void __launch_bounds__(128)
-latent_prepare_kernel(const T* __restrict__ proj, int ldp, T* __restrict__ q_rot, const int* __restrict__ positions,
-                      const int* __restrict__ slot_map, T* __restrict__ cache, const float* __restrict__ weight,
+latent_prepare_kernel(const T* __restrict__ proj, int ldp, T* __restrict__ q_rot, T* __restrict__ fresh,
+                      const int* __restrict__ positions, const int* __restrict__ slot_map, T* __restrict__ cache,
+                      const float* __restrict__ weight,
                       const float* __restrict__ freq, float eps, int H, int dim, int rot, int rank, int rot_dims) {
     __shared__ float scratch[33];
     pdl_trigger();
@@ -53,6 +55,11 @@ latent_prepare_kernel(const T* __restrict__ proj, int ldp, T* __restrict__ q_rot
     const float scale = 1.f / sqrtf(ss / (float)rank + eps);
     for (int i = threadIdx.x; i < rank; i += blockDim.x) kept[i] = from_float<T>(to_float(latent[i]) * scale * weight[i]);
     rotate_pairs(latent + rank, kept + rank, rot, rot_dims, position, freq, (int)threadIdx.x, (int)blockDim.x);
+    if (fresh) {  // the same row once more, token by token, for whoever wants the step's own rows side by side
+        __syncthreads();
+        T* copy = fresh + (size_t)t * (rank + rot);
+        for (int i = threadIdx.x; i < rank + rot; i += blockDim.x) copy[i] = kept[i];
+    }
 }
 
 // Attention with unit-RMS queries and keys.  qkv row: [H x dk queries | KV x dk keys | KV x dv values].
@@ -98,7 +105,7 @@ unit_norm_kv_write_kernel(T* __restrict__ qkv, int ld, const int* __restrict__ s
 
 }  // namespace
 
-LLM_EXPORT int llm_latent_prepare(const void* proj, int dtype, int ldp, void* q_rot, const int* positions,
+LLM_EXPORT int llm_latent_prepare(const void* proj, int dtype, int ldp, void* q_rot, void* fresh, const int* positions,
                                   const int* slot_map, void* cache, const float* weight, const float* freq, float eps, int n,
                                   int H, int dim, int rot, int rank, int rot_dims, cudaStream_t stream) {
     if (n <= 0) return 0;
@@ -107,10 +114,10 @@ LLM_EXPORT int llm_latent_prepare(const void* proj, int dtype, int ldp, void* q_
         return LLM_ERR_BAD_ARGUMENT;
     if (dtype == LLM_F32)
         return launch_pdl(latent_prepare_kernel<float>, dim3(n), dim3(128), 0, stream, (const float*)proj, ldp, (float*)q_rot,
-                          positions, slot_map, (float*)cache, weight, freq, eps, H, dim, rot, rank, rot_dims);
+                          (float*)fresh, positions, slot_map, (float*)cache, weight, freq, eps, H, dim, rot, rank, rot_dims);
     if (dtype == LLM_BF16)
         return launch_pdl(latent_prepare_kernel<__nv_bfloat16>, dim3(n), dim3(128), 0, stream, (const __nv_bfloat16*)proj, ldp,
-                          (__nv_bfloat16*)q_rot, positions, slot_map, (__nv_bfloat16*)cache, weight, freq, eps, H, dim, rot,
+                          (__nv_bfloat16*)q_rot, (__nv_bfloat16*)fresh, positions, slot_map, (__nv_bfloat16*)cache, weight, freq, eps, H, dim, rot,
                           rank, rot_dims);
     return LLM_ERR_BAD_ARGUMENT;
 }

@@ -83,10 +83,66 @@ group_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, fl
     }
 }
 
+// The same with a CTA of 128 threads per (row, group) and the part in registers, for steps of few rows (a warp per part
+// would walk a part of a thousand elements in 8 dependent trips to memory): parts of at most 4,096 elements, a
+// multiple of 4 long.
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(128)
+group_rmsnorm_wide_kernel(float* __restrict__ resid, const TD* __restrict__ delta, float alpha, const float* __restrict__ weight,
+                          float eps, int groups, const int* __restrict__ rows, TO* __restrict__ out, int hidden) {
+    __shared__ float scratch[33];
+    constexpr int NV = 8;
+    pdl_trigger();
+    const int o = blockIdx.x / groups, g = blockIdx.x - o * groups, len = hidden / groups, t4 = threadIdx.x * 4;
+    const float* w = weight + (size_t)g * len;
+    float wv[NV][4];
+#pragma unroll
+    for (int j = 0; j < NV; ++j)  // the weights do not depend on the kernel in front
+        if (t4 + j * 512 < len) load4(w + t4 + j * 512, wv[j]);
+    pdl_wait();
+    const int r = rows ? rows[o] : o;
+    float* x = resid + (size_t)r * hidden + (size_t)g * len;
+    const TD* d = delta ? delta + (size_t)r * hidden + (size_t)g * len : nullptr;
+    float v[NV][4], dv[NV][4];
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+        if (t4 + j * 512 < len) {
+            load4(x + t4 + j * 512, v[j]);
+            if (d) load4(d + t4 + j * 512, dv[j]);
+        }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+        if (t4 + j * 512 < len) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (d) v[j][e] = fmaf(alpha, dv[j][e], v[j][e]);
+                ss = fmaf(v[j][e], v[j][e], ss);
+            }
+        }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.f / sqrtf(ss / (float)len + eps);
+    TO* y = out + (size_t)o * hidden + (size_t)g * len;
+    const bool write_back = d && !rows;
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+        if (t4 + j * 512 < len) {
+            if (write_back) store4(x + t4 + j * 512, v[j]);
+            float n[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) n[e] = v[j][e] * scale * wv[j][e];
+            store4(y + t4 + j * 512, n);
+        }
+}
+
 template <typename TD, typename TO>
 int group_rmsnorm_launch(float* resid, const void* delta, float alpha, const float* weight, float eps, int groups,
                          const int* rows, void* out, int n_out, int hidden, cudaStream_t stream) {
     const long long items = (long long)n_out * groups;
+    const int len = hidden / groups;
+    if (items <= 1024 && (len & 3) == 0 && (hidden & 3) == 0 && len <= 4096 && len >= 256)
+        return launch_pdl(group_rmsnorm_wide_kernel<TD, TO>, dim3((unsigned)items), dim3(128), 0, stream, resid, (const TD*)delta,
+                          alpha, weight, eps, groups, rows, (TO*)out, hidden);
     const long long blocks = (items + NORM_WARPS - 1) / NORM_WARPS;
     if (blocks > 0x7fffffffLL) return LLM_ERR_UNSUPPORTED;
     return launch_pdl(group_rmsnorm_kernel<TD, TO>, dim3((unsigned)blocks), dim3(NORM_WARPS * 32), 0, stream, resid,

@@ -47,12 +47,13 @@ _SIGNATURES = {
     "llm_unary": [_vp, _i, _vp, _i, _i, _i, _i, _i, _f, _vp],
     "llm_gate_mul": [_vp, _ll, _ll, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
     "llm_mingru_scan": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
-    "llm_latent_prepare": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _vp],
+    "llm_latent_prepare": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _vp],
+    "llm_merge_two_parts": [_vp, _ll, _ll, _vp, _vp, _ll, _ll, _vp, _vp, _ll, _ll, _i, _i, _i, _vp],
     "llm_unit_norm_kv_write": [_vp, _i, _i, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "llm_attention_rows": [_vp, _ll, _ll, _i, _vp, _ll, _ll, _i, _vp, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _i, _i,
                            _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp],
     "llm_attention_rows_mma": [_vp, _ll, _ll, _i, _vp, _ll, _ll, _i, _vp, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _i,
-                               _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp, _vp],
+                               _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp, _i, _vp, _ll, _i, _vp, _vp],
     "llm_gemm_simt_batched": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _vp],
     "llm_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
 }
@@ -923,11 +924,12 @@ def mingru_scan(proj: torch.Tensor, bias_z, bias_u, states: torch.Tensor, state_
 
 
 def latent_prepare(proj: torch.Tensor, positions: torch.Tensor, slot_map: torch.Tensor, plane: torch.Tensor, weight: torch.Tensor,
-                   freq: torch.Tensor, eps: float, heads: int, dim: int, rot: int, rank: int) -> torch.Tensor:
+                   freq: torch.Tensor, eps: float, heads: int, dim: int, rot: int, rank: int, fresh: bool = False):
     """For latent attention, from a token's stacked projections ``proj`` = ``[heads x (dim | rot) | rank | rot | ...]``:
     the queries' rotated parts (interleaved pairs, angles ``position * freq[i]`` in 32-bit) are returned as
     ``[N, heads, rot]``; the latent, RMS-normed with ``weight``, and the rotated shared key part are written to the
-    token's slot of ``plane [pages, page_size, rank + rot]``."""
+    token's slot of ``plane [pages, page_size, rank + rot]``.  With ``fresh`` the written rows are also returned token by
+    token, ``[N, rank + rot]``: the result is then the pair ``(rotated query parts, rows)``."""
     _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] >= heads * (dim + rot) + rank + rot, "latent_prepare: proj rows are too short")
     _need(plane.dtype == proj.dtype and plane.is_contiguous() and plane.dim() == 3 and plane.shape[2] == rank + rot, "latent_prepare: the plane must be [pages, page_size, rank + rot] of the rows' type")
     _need(weight.dtype == torch.float32 and weight.numel() == rank and freq.dtype == torch.float32 and freq.is_contiguous(), "latent_prepare: weight [rank] and freq are float32")
@@ -935,10 +937,12 @@ def latent_prepare(proj: torch.Tensor, positions: torch.Tensor, slot_map: torch.
     _i32(slot_map, "slot_map")
     rot_dims = 2 * freq.numel()
     q_rot = torch.empty((proj.shape[0], heads, rot), dtype=proj.dtype, device=proj.device)
-    code = _launch("llm_latent_prepare", _ptr(proj), _code(proj.dtype), proj.stride(0), _ptr(q_rot), _ptr(positions), _ptr(slot_map),
-                   _ptr(plane), _ptr(weight), _ptr(freq), float(eps), proj.shape[0], heads, dim, rot, rank, rot_dims, _stream())
+    rows = torch.empty((proj.shape[0], rank + rot), dtype=proj.dtype, device=proj.device) if fresh else None
+    code = _launch("llm_latent_prepare", _ptr(proj), _code(proj.dtype), proj.stride(0), _ptr(q_rot), _ptr(rows), _ptr(positions),
+                   _ptr(slot_map), _ptr(plane), _ptr(weight), _ptr(freq), float(eps), proj.shape[0], heads, dim, rot, rank, rot_dims,
+                   _stream())
     _check(code, "latent_prepare")
-    return q_rot
+    return (q_rot, rows) if fresh else q_rot
 
 
 def unit_norm_kv_write(qkv: torch.Tensor, slot_map: torch.Tensor, pool: torch.Tensor, eps: float | None, heads: int, kv_heads: int,
@@ -975,10 +979,16 @@ def head_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 
 def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, page_table, page_size: int, ctx, *, num_heads: int,
-                   num_kv_heads: int, scale: float, window: int | None = None, slopes: torch.Tensor | None = None) -> torch.Tensor:
+                   num_kv_heads: int, scale: float, window: int | None = None, slopes: torch.Tensor | None = None,
+                   key_part: int = 0, keys1: int | None = None, k1_token: int = 0, fresh_d0: int = 0, want_stats: bool = False):
     """Attention in its general form: queries ``q0 [N, H, d0]`` and optionally ``q1 [N, H, d1]`` (lanes behind q0's),
     keys and values addressed by ``(page, head, token)`` strides in elements, an optional bias ``-slopes[h] * distance``.
-    Returns ``[N, H, value_dim]``."""
+    Returns ``[N, H, value_dim]``.
+
+    ``key_part`` (bfloat16 on the tensor cores only): 1 = only the keys cached before this step; 2 = only the step's own
+    tokens, whose keys and values lie token by token (``keys`` lanes ``[0, fresh_d0)`` per head, ``keys1`` the lanes
+    behind them, one row a token for all heads).  With ``want_stats`` the result is ``(out, stats [N, H, 2])``: each row's
+    maximum score and sum of exponentials (a row without keys: ``-inf, 0``, and an output that is not to be read), for :func:`merge_two_parts`."""
     n, d0 = q0.shape[0], q0.shape[2]
     d1 = 0 if q1 is None else q1.shape[2]
     _need(q0.stride(2) == 1 and (q1 is None or q1.stride(2) == 1), "attention_rows: queries need unit inner strides")
@@ -994,6 +1004,9 @@ def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, p
             longest = min(longest, window + ctx.max_query_len)
         ctas = -(-ctx.max_query_len * group // 64) * num_kv_heads * ctx.num_requests
         splits = max(1, min(-(-longest // 256), _sm_count() // ctas, 16, _SPLIT_SCRATCH_BYTES // (n * num_heads * value_dim * 4)))
+        if key_part or want_stats:
+            splits = 1
+        stats = torch.empty((n, num_heads, 2), dtype=torch.float32, device=q0.device) if want_stats else None
         part_o = part_ml = None
         if splits > 1:
             part_o = torch.empty((n * num_heads * splits * value_dim,), dtype=torch.float32, device=q0.device)
@@ -1003,13 +1016,14 @@ def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, p
             0 if q1 is None else q1.stride(1), d1, _ptr(out), out.stride(0), out.stride(1), keys, *k_strides, values, *v_strides,
             value_dim, _ptr(page_table), page_table.shape[1], _ptr(ctx.token_request), _ptr(ctx.cu_tokens), _ptr(ctx.context_lens),
             _ptr(slopes), n, ctx.num_requests, ctx.max_query_len, num_heads, num_kv_heads, page_size, int(window or 0), float(scale),
-            splits, _ptr(part_o), _ptr(part_ml), _stream(),
+            splits, _ptr(part_o), _ptr(part_ml), int(key_part), keys1, int(k1_token), int(fresh_d0), _ptr(stats), _stream(),
         )
         if code != 10002:
             add_launches(int(splits > 1))
             _check(code, "attention_rows (tensor cores)")
-            return out
+            return (out, stats) if want_stats else out
         add_launches(-1)  # a layout the kernel does not take: the general one below
+    _need(not key_part and not want_stats, "attention over a part of the keys runs on the tensor cores only (bfloat16, lanes in multiples of 16)")
     code = _launch(
         "llm_attention_rows", _ptr(q0), q0.stride(0), q0.stride(1), d0, _ptr(q1), 0 if q1 is None else q1.stride(0),
         0 if q1 is None else q1.stride(1), d1, _ptr(out), out.stride(0), out.stride(1), keys, *k_strides, values, *v_strides,
@@ -1020,17 +1034,57 @@ def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, p
     return out
 
 
+def merge_two_parts(o1: torch.Tensor, stats1: torch.Tensor, o2: torch.Tensor, stats2: torch.Tensor) -> torch.Tensor:
+    """Two parts of one softmax, each normalised by itself (``o [N, H, dv]`` bfloat16 with any token and head strides,
+    ``stats [N, H, 2]``), joined: ``(w1 o1 + w2 o2) / (w1 + w2)`` with ``w = sum * exp(maximum - M)``."""
+    _need(o1.shape == o2.shape and o1.dtype == o2.dtype == torch.bfloat16 and o1.stride(2) == 1 and o2.stride(2) == 1, "merge_two_parts: two bfloat16 [N, H, dv] outputs")
+    n, heads, dv = o1.shape
+    out = torch.empty((n, heads, dv), dtype=o1.dtype, device=o1.device)
+    code = _launch("llm_merge_two_parts", _ptr(o1), o1.stride(0), o1.stride(1), _ptr(stats1), _ptr(o2), o2.stride(0), o2.stride(1),
+                   _ptr(stats2), _ptr(out), out.stride(0), out.stride(1), n, heads, dv, _stream())
+    _check(code, "merge_two_parts")
+    return out
+
+
+# from this many tokens of a request in a step on, latent attention expands the step's own keys and values per head
+_LATENT_TWO_PART_MIN_TOKENS = 128
+
+
+def latent_two_parts(ctx, dtype: torch.dtype, *lanes: int) -> bool:
+    """Whether a step's latent attention runs in two parts (see parts/latent_attention.py): a bfloat16 step in which a
+    request brings many tokens, with every run of lanes a multiple of 16."""
+    return (dtype == torch.bfloat16 and not _FORCE_GENERIC_ATTENTION and ctx.max_query_len >= _LATENT_TWO_PART_MIN_TOKENS
+            and all(x % 16 == 0 for x in lanes))
+
+
 def latent_paged_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, plane: torch.Tensor, page_table: torch.Tensor, ctx, *,
-                           rank: int, scale: float, window: int | None = None) -> torch.Tensor:
+                           rank: int, scale: float, window: int | None = None, cached_only: bool = False):
     """Attention of every new token over its request's cached latents.  A cached row ``[rank | rot]`` is the key of
     every head (against the query ``[q_lat | q_rot]``) and, in its first ``rank`` lanes, the value.
-    ``plane [pages, page_size, rank + rot]``; returns ``[N, H, rank]``."""
+    ``plane [pages, page_size, rank + rot]``; returns ``[N, H, rank]``.  ``cached_only``: only the rows cached before
+    this step are seen, and the result is ``(out, stats)`` for :func:`merge_two_parts`."""
     _need(plane.dtype == q_lat.dtype and plane.is_contiguous() and plane.dim() == 3, "the plane must be contiguous [pages, page_size, width] of the query type")
     page_size, width = plane.shape[1], plane.shape[2]
     _need(q_lat.shape[2] == rank and q_lat.shape[2] + q_rot.shape[2] == width, "the queries do not match the cached rows")
     strides = (page_size * width, 0, width)
     return attention_rows(q_lat, q_rot, _ptr(plane), strides, _ptr(plane), strides, rank, page_table, page_size, ctx,
-                          num_heads=q_lat.shape[1], num_kv_heads=1, scale=scale, window=window)
+                          num_heads=q_lat.shape[1], num_kv_heads=1, scale=scale, window=window,
+                          key_part=1 if cached_only else 0, want_stats=cached_only)
+
+
+def fresh_latent_attention(q_plain: torch.Tensor, q_rot: torch.Tensor, kv: torch.Tensor, fresh: torch.Tensor, page_table: torch.Tensor,
+                           ctx, *, dim: int, value_dim: int, rank: int, scale: float, window: int | None = None):
+    """Attention of every new token over the step's own tokens of its request, with keys and values per head:
+    ``kv [N, H * dim | H * value_dim]`` (the latents' products with the two up matrices), the rotated shared key part in
+    ``fresh[:, rank:]``.  Returns ``(out [N, H, value_dim], stats)`` for :func:`merge_two_parts`."""
+    n, heads = q_plain.shape[0], q_plain.shape[1]
+    rot = fresh.shape[1] - rank
+    _need(kv.is_contiguous() and fresh.is_contiguous() and kv.shape[1] == heads * (dim + value_dim), "fresh_latent_attention: kv [N, H dim | H vdim]")
+    element = kv.element_size()
+    return attention_rows(q_plain, q_rot, kv.data_ptr(), (0, dim, kv.stride(0)), kv.data_ptr() + heads * dim * element,
+                          (0, value_dim, kv.stride(0)), value_dim, page_table, 1, ctx, num_heads=heads, num_kv_heads=heads,
+                          scale=scale, window=window, key_part=2, keys1=fresh.data_ptr() + rank * element, k1_token=rank + rot,
+                          fresh_d0=dim, want_stats=True)
 
 
 def biased_paged_attention(qkv: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor, ctx, *, num_heads: int, num_kv_heads: int,

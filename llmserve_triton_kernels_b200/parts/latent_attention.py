@@ -10,7 +10,10 @@ is ``[W_uk[h] c | k_rot]`` with a rotated part ``k_rot`` (``rot_dim`` lanes) tha
 so that attention runs over the cached rows themselves: every head reads the same row as its key (all
 ``rank + rot_dim`` lanes) and as its value (the first ``rank``).  The latent is RMS-normed (a weight of its own)
 before it is cached; rotary positions use the interleaved layout (lanes 2i and 2i+1 form a pair) with angles
-computed in 32-bit from the position; the concatenated heads are multiplied by ``sigmoid(W_g x)`` before the output
+computed in 32-bit from the position.  In a bfloat16 step in which a request brings many tokens the softmax is taken in
+two parts that a last kernel joins: the rows cached before the step as above, and the step's own tokens with keys and
+values per head (``W_uk c``, ``W_uv c``: one product for all new tokens), which takes a third of the arithmetic of
+attention over the latents.  The concatenated heads are multiplied by ``sigmoid(W_g x)`` before the output
 projection.  Sizes, the softmax scale, the rotary base and the names of the tensors are parameters.
 """
 
@@ -55,7 +58,7 @@ class LatentAttention(Mixer):
         self.output_gate = bool(output_gate)
         self.window = None if window is None else int(window)
         self.names = {**_NAMES, **(tensor_names or {})}
-        self.w_in = self.w_uk_t = self.w_uv = self.w_out = self.latent_weight = self.freq = None
+        self.w_in = self.w_uk_t = self.w_uv = self.w_up = self.w_out = self.latent_weight = self.freq = None
 
     def tensors(self) -> dict[str, TensorSpec]:
         H, n = self.num_heads, self.names
@@ -78,6 +81,8 @@ class LatentAttention(Mixer):
         # W_uk per head, turned so that it multiplies the query: [H, rank, head_dim]
         self.w_uk_t = tensors[n["up_k"]].to(dtype).view(H, self.head_dim, self.rank).transpose(1, 2).contiguous().to(device)
         self.w_uv = tensors[n["up_v"]].to(dtype).view(H, self.value_dim, self.rank).contiguous().to(device)
+        # both up matrices stacked, for the keys and values of a step's own tokens: [H dim | H vdim, rank]
+        self.w_up = torch.cat([tensors[n["up_k"]].to(dtype), tensors[n["up_v"]].to(dtype)], dim=0).to(device).contiguous()
         self.w_out = tensors[n["out"]].to(device=device, dtype=dtype).contiguous()
         self.latent_weight = tensors[n["latent_norm"]].to(device=device, dtype=torch.float32).contiguous()
         pairs = torch.arange(self.rotary_dims // 2, dtype=torch.float64)
@@ -89,15 +94,29 @@ class LatentAttention(Mixer):
     def forward(self, x, ctx, cache, sink=None):
         H, dim, rot, rank = self.num_heads, self.head_dim, self.rot_dim, self.rank
         proj = ops.linear(x, self.w_in)  # [N, H (dim | rot) | rank | rot | H vdim]
-        q_rot = ops.latent_prepare(
-            proj, ctx.positions, cache.slot_map, cache.pool, self.latent_weight, self.freq, self.norm_eps, H, dim, rot, rank
+        two_parts = ops.latent_two_parts(ctx, proj.dtype, dim, rot, rank, self.value_dim)
+        prepared = ops.latent_prepare(
+            proj, ctx.positions, cache.slot_map, cache.pool, self.latent_weight, self.freq, self.norm_eps, H, dim, rot, rank,
+            fresh=two_parts,
         )
+        q_rot, fresh = prepared if two_parts else (prepared, None)
         q_plain = proj.as_strided((proj.shape[0], H, dim), (proj.stride(0), dim + rot, 1), proj.storage_offset())
         q_lat = ops.head_linear(q_plain, self.w_uk_t)  # [N, H, rank]
-        mixed = ops.latent_paged_attention(
-            q_lat, q_rot, cache.pool, cache.page_table, ctx, rank=rank, scale=self.scale, window=self.window
-        )
-        heads = ops.head_linear(mixed, self.w_uv)  # [N, H, vdim]
+        if two_parts:
+            cached, cached_stats = ops.latent_paged_attention(
+                q_lat, q_rot, cache.pool, cache.page_table, ctx, rank=rank, scale=self.scale, window=self.window, cached_only=True
+            )
+            kv = ops.linear(fresh[:, :rank], self.w_up)  # keys and values of the step's own tokens, head by head
+            own, own_stats = ops.fresh_latent_attention(
+                q_plain, q_rot, kv, fresh, cache.page_table, ctx, dim=dim, value_dim=self.value_dim, rank=rank, scale=self.scale,
+                window=self.window,
+            )
+            heads = ops.merge_two_parts(own, own_stats, ops.head_linear(cached, self.w_uv), cached_stats)
+        else:
+            mixed = ops.latent_paged_attention(
+                q_lat, q_rot, cache.pool, cache.page_table, ctx, rank=rank, scale=self.scale, window=self.window
+            )
+            heads = ops.head_linear(mixed, self.w_uv)  # [N, H, vdim]
         if self.output_gate:
             out = ops.gate_mul(heads, proj[:, H * (dim + rot) + rank + rot :], "sigmoid")
         else:

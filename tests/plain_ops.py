@@ -212,7 +212,7 @@ def _rotate_interleaved(x, positions, freq):
     return out
 
 
-def latent_prepare(proj, positions, slot_map, plane, weight, freq, eps, heads, dim, rot, rank):
+def latent_prepare(proj, positions, slot_map, plane, weight, freq, eps, heads, dim, rot, rank, fresh=False):
     n = proj.shape[0]
     q = proj[:, : heads * (dim + rot)].float().view(n, heads, dim + rot)
     q_rot = _rotate_interleaved(q[..., dim:], positions, freq).to(proj.dtype)
@@ -223,7 +223,11 @@ def latent_prepare(proj, positions, slot_map, plane, weight, freq, eps, heads, d
     page_size = plane.shape[1]
     page, off = (slot_map // page_size).long(), (slot_map % page_size).long()
     plane[page, off] = torch.cat((latent, k_rot), dim=-1).to(plane.dtype)
-    return q_rot
+    return (q_rot, plane[page, off].clone()) if fresh else q_rot
+
+
+def latent_two_parts(ctx, dtype, *lanes):
+    return False  # the plain operations know one way only
 
 
 def unit_norm_kv_write(qkv, slot_map, pool, eps, heads, kv_heads, key_dim, value_dim):
@@ -296,6 +300,7 @@ ALL = (
     "gate_mul",
     "mingru_scan",
     "latent_prepare",
+    "latent_two_parts",
     "unit_norm_kv_write",
     "head_linear",
     "latent_paged_attention",

@@ -296,3 +296,38 @@ def test_plan_orders_a_loop_with_caches_of_its_own_and_names_every_tensor():
     specs = model.cache_specs()
     assert len(specs) == 8 and len({id(s) for s in specs}) == 8
     assert model.graph_safe
+
+
+# --------------------------------------------------------------------------------------------- long portions
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["ones", "whole_loop", "head_loop"])
+def test_latent_attention_in_two_parts_from_two_tokens_on(name, engine, monkeypatch):
+    """In bfloat16 a step in which a request brings many tokens joins two partial softmaxes (the cached rows, and the
+    step's own tokens with keys and values per head); here every portion of two tokens and more goes that way, beside
+    decoded tokens, with and without rows cached before."""
+    from llmserve_triton_kernels_b200 import ops
+
+    monkeypatch.setattr(ops, "_LATENT_TWO_PART_MIN_TOKENS", 2)
+    test_ways_of_cutting(name, "cuda-bfloat16", engine)
+    if name == "head_loop":
+        test_mixed_batches_with_pages_and_slots_used_again(name, "cuda-bfloat16", engine)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_portions(dtype, engine):
+    """Prompts of some hundred tokens, whole and in two long portions beside a decoding request."""
+    where = f"cuda-{dtype}"
+    engine(where)
+    cfg = configs.HEAD_LOOP
+    model, tensors, dtype = make_model(cfg, 23, where)
+    reqs = tokens_for(cfg["vocab"], [330, 40], 6)
+    exp = expected_of(cfg, tensors, reqs)
+    d = Driver(model, num_pages=100, page_size=8)
+    d.run([("r0", reqs["r0"])], end=["r0"])
+    check(d.got, exp, dtype, "whole")
+    d.got.clear()
+    d.run([("r1", reqs["r1"][:39])])
+    d.run([("r0", reqs["r0"][:150]), ("r1", reqs["r1"][39:])], end=["r1"])
+    d.run([("r0", reqs["r0"][150:])], end=["r0"])
+    check(d.got, exp, dtype, "two long portions")
