@@ -9,19 +9,21 @@ namespace {
 
 // Interleaved rotary layout: lanes (2i, 2i + 1) of the first `rot_dims` lanes turn by position * freq[i]; the lanes
 // behind them pass unchanged.
+// `turn` holds (cos, sin) of every pair's angle, worked out once per token.
 template <typename T>
 __device__ __forceinline__ void rotate_pairs(const T* __restrict__ src, T* __restrict__ dst, int lanes, int rot_dims,
-                                             float position, const float* __restrict__ freq, int first, int step) {
+                                             const float2* __restrict__ turn, int first, int step) {
     const int pairs = rot_dims >> 1;
     for (int i = first; i < pairs; i += step) {
-        float s, c;
-        sincosf(position * freq[i], &s, &c);
+        const float c = turn[i].x, s = turn[i].y;
         const float u = to_float(src[2 * i]), v = to_float(src[2 * i + 1]);
         dst[2 * i] = from_float<T>(u * c - v * s);
         dst[2 * i + 1] = from_float<T>(v * c + u * s);
     }
     for (int i = rot_dims + first; i < lanes; i += step) dst[i] = src[i];
 }
+
+constexpr int MAX_TURNS = 320;  // pairs of a rotated part of at most 640 lanes
 
 // Latent attention.  proj row: [H x (dim | rot) queries][rank latent | rot shared key part][...].
 //   q_rot[t, h, :]   = rotate(proj query h's last rot lanes)
@@ -35,15 +37,23 @@ latent_prepare_kernel(const T* __restrict__ proj, int ldp, T* __restrict__ q_rot
                       const float* __restrict__ weight,
                       const float* __restrict__ freq, float eps, int H, int dim, int rot, int rank, int rot_dims) {
     __shared__ float scratch[33];
+    __shared__ float2 turn[MAX_TURNS];
     pdl_trigger();
     const int t = blockIdx.x;
     const float position = (float)positions[t];
     const size_t slot = (size_t)slot_map[t];
+    // the angles depend on the token alone: every head and the shared key part turn by the same ones
+    for (int i = threadIdx.x; i < (rot_dims >> 1); i += blockDim.x) {
+        float s, c;
+        sincosf(position * freq[i], &s, &c);
+        turn[i] = make_float2(c, s);
+    }
+    __syncthreads();
     pdl_wait();
     const T* row = proj + (size_t)t * ldp;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     for (int h = warp; h < H; h += warps)
-        rotate_pairs(row + (size_t)h * (dim + rot) + dim, q_rot + ((size_t)t * H + h) * rot, rot, rot_dims, position, freq, lane, 32);
+        rotate_pairs(row + (size_t)h * (dim + rot) + dim, q_rot + ((size_t)t * H + h) * rot, rot, rot_dims, turn, lane, 32);
     const T* latent = row + (size_t)H * (dim + rot);
     T* kept = cache + slot * (size_t)(rank + rot);
     float ss = 0.f;
@@ -54,7 +64,7 @@ latent_prepare_kernel(const T* __restrict__ proj, int ldp, T* __restrict__ q_rot
     ss = block_sum(ss, scratch);
     const float scale = 1.f / sqrtf(ss / (float)rank + eps);
     for (int i = threadIdx.x; i < rank; i += blockDim.x) kept[i] = from_float<T>(to_float(latent[i]) * scale * weight[i]);
-    rotate_pairs(latent + rank, kept + rank, rot, rot_dims, position, freq, (int)threadIdx.x, (int)blockDim.x);
+    rotate_pairs(latent + rank, kept + rank, rot, rot_dims, turn, (int)threadIdx.x, (int)blockDim.x);
     if (fresh) {  // the same row once more, token by token, for whoever wants the step's own rows side by side
         __syncthreads();
         T* copy = fresh + (size_t)t * (rank + rot);
@@ -109,7 +119,7 @@ LLM_EXPORT int llm_latent_prepare(const void* proj, int dtype, int ldp, void* q_
                                   const int* slot_map, void* cache, const float* weight, const float* freq, float eps, int n,
                                   int H, int dim, int rot, int rank, int rot_dims, cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (H <= 0 || dim < 0 || rot < 0 || rank <= 0 || rot_dims < 0 || rot_dims > rot || (rot_dims & 1) ||
+    if (H <= 0 || dim < 0 || rot < 0 || rank <= 0 || rot_dims < 0 || rot_dims > rot || (rot_dims & 1) || rot_dims > 2 * MAX_TURNS ||
         ldp < H * (dim + rot) + rank + rot)
         return LLM_ERR_BAD_ARGUMENT;
     if (dtype == LLM_F32)
