@@ -14,6 +14,9 @@ cache of the live requests) to its time; ``points`` holds decode at batch 1 and 
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from an earlier
 measurement on the same pool (and the line says which).
 
+``python bench.py --design nurolorn-small|nurolorn-1b`` prints, instead of the line, prefill and decode throughput of that
+Nurolorn configuration beside a Llama of equal width, depth and feed-forward size, and the design's kernels against their rooflines.
+
 ``python bench.py --sweep [--steps K]`` prints no JSON line but two tables: decode steps over batch sizes and
 context lengths, and prefills over prompt lengths, timed the same way.
 """

@@ -53,4 +53,11 @@ HEAD_LOOP = config(
     vocab=200, width=128, groups=2, mult=0.7, logit_scale=2.0, loop=(0, 3, 2),
 )
 
-ALL = {"odd": ODD, "ones": ONES, "whole_loop": WHOLE_LOOP, "head_loop": HEAD_LOOP}
+# the smallest of everything: one head, keys of two lanes, values of one, a state of one channel, norm parts of five
+# elements, a loop over one layer that runs four times
+SMALLEST = config(
+    [latent(1, 2, 2, 1, 4, 0.7, base=3.0), mingru(1, ff=8), window(3, 3, 4, 2, 2, 0.6), latent(2, 6, 4, 3, 8, 0.5, dims=2, ff=12)],
+    vocab=23, width=40, groups=8, mult=1.3, logit_scale=3.0, loop=(1, 2, 4),
+)
+
+ALL = {"smallest": SMALLEST, "odd": ODD, "ones": ONES, "whole_loop": WHOLE_LOOP, "head_loop": HEAD_LOOP}

@@ -331,3 +331,72 @@ def test_long_portions(dtype, engine):
     d.run([("r0", reqs["r0"][:150]), ("r1", reqs["r1"][39:])], end=["r1"])
     d.run([("r0", reqs["r0"][150:])], end=["r0"])
     check(d.got, exp, dtype, "two long portions")
+
+
+# --------------------------------------------------------------------------------------------- the replay program
+def _replay_trace(cfg, seed=31):
+    import trace_tools
+
+    reqs = tokens_for(cfg["vocab"], [41, 6, 75, 20, 33], seed)
+    trace = trace_tools.Trace()
+    flat = {}
+    for r, t in list(reqs.items())[:2]:
+        for tag, make in (("w", trace_tools.whole), ("d", lambda n, x: trace_tools.decode_tail(n, x, tail=5)), ("p", trace_tools.portions)):
+            trace.extend(make(f"{tag}.{r}", t))
+            flat[f"{tag}.{r}"] = t
+    both = {**{f"m.{r}": t for r, t in reqs.items()}, **{f"m.{r}'": t for r, t in reqs.items()}}
+    trace.extend(trace_tools.mixed(both, {k: max(1, len(v) - 4) for k, v in both.items()}, chunk=9, live=4))
+    flat.update(both)
+    return trace, flat
+
+
+def _check_replay(got, cfg, tensors, flat, dtype):
+    done = {}
+    rows = {}
+    for (req, pos), row in got.items():
+        key = tuple(flat[req])
+        if key not in done:
+            done[key] = plain_nurolorn.forward(cfg, tensors, flat[req])
+        rows[(req, pos)] = (torch.from_numpy(row.copy()), done[key][pos])
+    tol = F32_TOL if dtype == "float32" else BF16_TOL
+    assert rows
+    for (req, pos), (row, ref) in sorted(rows.items()):
+        d = row.double() - ref
+        err = float((d - d.mean()).pow(2).mean().sqrt() / ref.pow(2).mean().sqrt().clamp_min(1e-6))
+        assert err <= tol, f"first wrong row: request {req!r} position {pos}: error {err:.3e} > {tol:.1e}"
+
+
+def _model_folder(cfg, tmp_path, seed=3, std=0.12):
+    import llmserve_triton_kernels_b200.models  # noqa: F401
+    from llmserve_triton_kernels_b200.config import architecture_of
+    from llmserve_triton_kernels_b200.weights import write_random_model
+    from llmserve_triton_kernels_b200.weights.loader import read_safetensors
+
+    folder = write_random_model(tmp_path / "model", architecture_of(cfg).config_class.from_dict(cfg), seed=seed, std=std)
+    return folder, read_safetensors(folder)
+
+
+def test_replay_program_host_side(tmp_path, engine):
+    """A model folder of the design through the replay program in this process, over the plain operations: the folder's
+    config.json picks the model class, steps come as JSON lines, logits go to files, pages and slots are used again."""
+    import trace_tools
+
+    engine("plain")
+    cfg = configs.ODD
+    folder, tensors = _model_folder(cfg, tmp_path)
+    trace, flat = _replay_trace(cfg)
+    got = trace_tools.run_trace_inprocess(folder, "float32", trace, tmp_path / "out", device="cpu", page_size=4)
+    _check_replay(got, cfg, tensors, flat, "float32")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["odd", "head_loop"])
+def test_replay_program_as_a_user_starts_it(name, dtype, tmp_path):
+    import trace_tools
+
+    cfg = configs.ALL[name]
+    folder, tensors = _model_folder(cfg, tmp_path)
+    trace, flat = _replay_trace(cfg)
+    got = trace_tools.run_trace(folder, dtype, trace, tmp_path / "out")
+    _check_replay(got, cfg, tensors, flat, dtype)

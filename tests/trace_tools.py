@@ -201,7 +201,8 @@ def run_trace_inprocess(model_dir, dtype: str, trace: Trace, out_dir, device: st
     finally:
         sys.stdin, sys.stdout = stdin, stdout
     assert [l for l in said if l] == [f"done {s['step']}" for s in trace.steps]
-    vocab = json.loads((Path(model_dir) / "config.json").read_text())["vocab_size"]
+    cfg = json.loads((Path(model_dir) / "config.json").read_text())
+    vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
     got = {}
     for s in trace.steps:
         rows = trace.rows.get(s["step"])
