@@ -192,18 +192,22 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
             }
         }
         // scale, bias, mask (scores in units of log 2 from here on); the tile's maximum per row
-        float tile_max[2] = {-INFINITY, -INFINITY};
+        // (maxima and sums are kept in two halves per row, joined at the end: half as long a chain of dependent operations)
+        float part_max[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}};
         const bool whole = j0 >= warp_lo && j0 + BN - 1 <= warp_hi;  // every row of the warp sees every key of the tile
+        const bool biased = a.slopes != nullptr;
 #pragma unroll
         for (int nb = 0; nb < BN / 8; ++nb)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int e = c >> 1, j = j0 + nb * 8 + (lane & 3) * 2 + (c & 1);
-                float v = fmaf(s[nb][c], scale2, -slope[e] * (float)(pos[e] - j));
+                float v = s[nb][c] * scale2;
+                if (biased) v -= slope[e] * (float)(pos[e] - j);
                 if (!whole) v = (j >= lo[e] && j <= hi[e]) ? v : -INFINITY;
                 s[nb][c] = v;
-                tile_max[e] = fmaxf(tile_max[e], v);
+                part_max[e][nb & 1] = fmaxf(part_max[e][nb & 1], v);
             }
+        float tile_max[2] = {fmaxf(part_max[0][0], part_max[0][1]), fmaxf(part_max[1][0], part_max[1][1])};
         float rescale[2], m_use[2];
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
@@ -221,14 +225,17 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
                 o[i][0] *= rescale[0]; o[i][1] *= rescale[0];
                 o[i][2] *= rescale[1]; o[i][3] *= rescale[1];
             }
+        float part_sum[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
 #pragma unroll
         for (int nb = 0; nb < BN / 8; ++nb)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const float p = exp2f(s[nb][c] - m_use[c >> 1]);
                 s[nb][c] = p;
-                l[c >> 1] += p;
+                part_sum[c >> 1][nb & 1] += p;
             }
+        l[0] += part_sum[0][0] + part_sum[0][1];
+        l[1] += part_sum[1][0] + part_sum[1][1];
         // O += P V
 #pragma unroll
         for (int kb = 0; kb < BN / 16; ++kb) {
@@ -353,6 +360,55 @@ merge_two_parts_kernel(const bf16* __restrict__ o1, long long o1_token, long lon
     }
 }
 
+// For steps of few rows whose keys were cut over `splits` CTAs: the merge of the partial results, the product with a
+// per-head matrix w [H, n_out, dv] (the value up-projection of latent attention) and an optional sigmoid gate, in one
+// kernel; one CTA per (token, head).  out[t, h * n_out + e] = gate(g[t, h * n_out + e]) * sum_r w[h, e, r] merged[r].
+__global__ void __launch_bounds__(128)
+merge_project_gate_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits,
+                          const bf16* __restrict__ w, const bf16* __restrict__ gate, int ldg, bf16* __restrict__ out, int H,
+                          int dv, int n_out) {
+    extern __shared__ float merged[];  // dv floats, then the splits' weights
+    float* weights = merged + dv;
+    const int item = blockIdx.x, t = item / H, h = item - t * H, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    pdl_trigger();
+    pdl_wait();
+    const float* ml = part_ml + (size_t)item * splits * 2;
+    if (warp == 0) {
+        const float ms = lane < splits ? ml[2 * lane] : -INFINITY, ls = lane < splits ? ml[2 * lane + 1] : 0.f;
+        const float M = warp_max(ms);
+        const float ws = ms == -INFINITY ? 0.f : exp2f(ms - M);
+        const float inv = 1.f / warp_sum(ws * ls);
+        if (lane < splits) weights[lane] = ws * inv;
+    }
+    __syncthreads();
+    const float* po = part_o + (size_t)item * splits * dv;
+    for (int r = threadIdx.x; r < dv; r += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float ws = weights[s];
+            if (ws != 0.f) acc = fmaf(ws, po[(size_t)s * dv + r], acc);
+        }
+        merged[r] = acc;
+    }
+    __syncthreads();
+    const bf16* wh = w + (size_t)h * n_out * dv;
+    for (int e = warp; e < n_out; e += 4) {
+        const bf16* row = wh + (size_t)e * dv;
+        float acc = 0.f;
+        for (int r = lane * 2; r < dv; r += 64) {
+            const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(row + r);
+            acc = fmaf(__low2float(v), merged[r], acc);
+            acc = fmaf(__high2float(v), merged[r + 1], acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            const size_t col = (size_t)h * n_out + e;
+            if (gate) acc *= 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)t * ldg + col])));
+            out[(size_t)t * H * n_out + col] = __float2bfloat16_rn(acc);
+        }
+    }
+}
+
 template <int DV_MAX, int BN, int BM = 64>
 int launch(const RowsArgs<bf16>& a, int requests, int max_query_len, int splits, float* part_o, float* part_ml, size_t smem,
            cudaStream_t stream) {
@@ -432,10 +488,21 @@ LLM_EXPORT int llm_attention_rows_mma(const void* q0, long long q0_token, long l
     else
         code = wide ? launch<256, 64>(a, requests, max_query_len, splits, part_o, part_ml, smem, stream)
                     : launch<256, 32>(a, requests, max_query_len, splits, part_o, part_ml, smem, stream);
-    if (code != 0 || splits == 1) return code;
+    if (code != 0 || splits == 1 || out == nullptr) return code;  // no out: the partial results are what the caller wants
     const long long items = (long long)n_tokens * H;
     return launch_pdl(attention_rows_merge_kernel, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, (const float*)part_o,
                       (const float*)part_ml, (bf16*)out, out_token, out_head, n_tokens, H, dv, splits);
+}
+
+// The partial results of llm_attention_rows_mma with splits > 1 and no out (part_o, part_ml), merged, multiplied per head
+// by w [H, n_out, dv] and by sigmoid(gate [n, H * n_out], row pitch ldg; null: no gate) -> out [n, H * n_out].  dv even.
+LLM_EXPORT int llm_merge_project_gate(const float* part_o, const float* part_ml, int splits, const void* w, const void* gate,
+                                      int ldg, void* out, int n_tokens, int H, int dv, int n_out, cudaStream_t stream) {
+    if (n_tokens <= 0 || H <= 0) return 0;
+    if (splits < 1 || splits > 32 || dv <= 0 || (dv & 1) || n_out <= 0 || ((uintptr_t)w & 3)) return LLM_ERR_BAD_ARGUMENT;
+    const size_t smem = (size_t)(dv + 32) * sizeof(float);
+    return launch_pdl(merge_project_gate_kernel, dim3((unsigned)(n_tokens * H)), dim3(128), smem, stream, part_o, part_ml, splits,
+                      (const bf16*)w, (const bf16*)gate, ldg, (bf16*)out, H, dv, n_out);
 }
 
 // Two parts of one softmax, each normalised by itself (o [n, H, dv] bfloat16 with token and head strides, stats [n, H, 2] =

@@ -46,6 +46,10 @@ class StepContext:
     # True for the fixed buffers of a captured decode step: one token per request, every row's logits wanted,
     # the same addresses at every replay (a model may then build a plan for the step once and keep it)
     static_decode: bool = False
+    # True if every request of the step starts at position 0 (whole prompts, or first portions): nothing was cached for
+    # them before the step, which a mixer may use to leave out the work over cached rows.  A graph is captured for one
+    # value of this and replayed only for steps of the same kind.
+    fresh_requests: bool = False
 
 
 def pack_step(entries: list[StepEntry], lengths: list[int], state_slots: np.ndarray, group_arrays, device):
@@ -100,6 +104,7 @@ def pack_step(entries: list[StepEntry], lengths: list[int], state_slots: np.ndar
         host_state_slots=state_slots.tolist(),
         max_query_len=max(counts),
         max_context_len=int(ctx_lens.max()),
+        fresh_requests=all(s == 0 for s in lengths),
     )
     group_tensors = []
     for g, (table, _) in enumerate(group_arrays):

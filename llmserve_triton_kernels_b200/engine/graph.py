@@ -30,10 +30,11 @@ def _pad4(n: int) -> int:
 
 
 class StepGraph:
-    def __init__(self, model, cache, counts: tuple[int, ...], wants: tuple[tuple[int, ...], ...], owner=None):
+    def __init__(self, model, cache, counts: tuple[int, ...], wants: tuple[tuple[int, ...], ...], owner=None, fresh_requests: bool = False):
         """``counts[r]``: tokens that request r of the step brings; ``wants[r]``: the places among them whose
         logits are returned.  ``owner``: whoever keeps the graphs (an object with an attribute ``graph_pool``): the
-        graphs of one owner share one memory pool, that of the first one captured."""
+        graphs of one owner share one memory pool, that of the first one captured.  ``fresh_requests``: the graph is for
+        steps in which every request starts at position 0 (``StepContext.fresh_requests``)."""
         self.model, self.cache, self.owner = model, cache, owner
         self.counts, self.wants = tuple(counts), tuple(tuple(w) for w in wants)
         R, N = len(self.counts), sum(self.counts)
@@ -73,6 +74,7 @@ class StepGraph:
             token_ids=d(0), positions=d(1), token_request=d(2), cu_tokens=d(3), context_lens=d(4), logit_rows=d(5),
             state_slots=d(6), host_cu_tokens=cu.tolist(), host_context_lens=None, host_state_slots=None,
             max_query_len=max(self.counts), max_context_len=self.max_positions, static_decode=self.decode_only,
+            fresh_requests=bool(fresh_requests),
         )
         group_tensors = []
         for g, w in enumerate(self.widths):

@@ -69,7 +69,7 @@ class StepFunction:
         lengths = [cache.lengths[req] for req, _ in pairs]
         self.last_was_graph = False
         if self.use_graphs:
-            graph = self._graph_for(entries)
+            graph = self._graph_for(entries, fresh=all(n == 0 for n in lengths))
             if graph is not None:
                 tokens = [t for e in entries for t in e.tokens]
                 return self._replay(graph, pairs, tokens, lengths, state_slots, group_arrays)
@@ -86,14 +86,15 @@ class StepFunction:
             graph = self.graphs[requests] = StepGraph(self.model, self.cache, (1,) * requests, ((0,),) * requests, owner=self)
         return graph
 
-    def _graph_for(self, entries: list[StepEntry]) -> StepGraph | None:
+    def _graph_for(self, entries: list[StepEntry], fresh: bool = False) -> StepGraph | None:
         """The graph of this step's shape, or None if the step runs kernel by kernel (a shape seen for the first
-        time, or too large to be worth it)."""
+        time, or too large to be worth it).  ``fresh``: every request of the step starts at position 0; such steps have
+        graphs of their own, in which a mixer may leave out what it does over cached rows."""
         if all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            return self._decode_graph(len(entries))
+            return self._decode_graph(len(entries))  # its context says nothing about where the requests start
         if sum(len(e.tokens) for e in entries) > self.MAX_GRAPH_TOKENS:
             return None
-        shape = tuple((len(e.tokens), tuple(e.want)) for e in entries)
+        shape = (fresh,) + tuple((len(e.tokens), tuple(e.want)) for e in entries)
         graph = self.shape_graphs.pop(shape, None)
         if graph is None:
             seen = self._seen_shapes[shape] = self._seen_shapes.get(shape, 0) + 1
@@ -101,7 +102,8 @@ class StepFunction:
                 self._seen_shapes.clear()
             if seen < 2:
                 return None
-            graph = StepGraph(self.model, self.cache, tuple(n for n, _ in shape), tuple(w for _, w in shape), owner=self)
+            graph = StepGraph(self.model, self.cache, tuple(n for n, _ in shape[1:]), tuple(w for _, w in shape[1:]), owner=self,
+                              fresh_requests=fresh)
             while len(self.shape_graphs) >= self.MAX_SHAPE_GRAPHS:
                 self.shape_graphs.pop(next(iter(self.shape_graphs)))
         self.shape_graphs[shape] = graph  # most recently used last

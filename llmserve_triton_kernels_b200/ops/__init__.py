@@ -48,6 +48,7 @@ _SIGNATURES = {
     "llm_gate_mul": [_vp, _ll, _ll, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
     "llm_mingru_scan": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "llm_latent_prepare": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _vp],
+    "llm_merge_project_gate": [_vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
     "llm_merge_two_parts": [_vp, _ll, _ll, _vp, _vp, _ll, _ll, _vp, _vp, _ll, _ll, _i, _i, _i, _vp],
     "llm_unit_norm_kv_write": [_vp, _i, _i, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "llm_attention_rows": [_vp, _ll, _ll, _i, _vp, _ll, _ll, _i, _vp, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _i, _i,
@@ -980,7 +981,8 @@ def head_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, page_table, page_size: int, ctx, *, num_heads: int,
                    num_kv_heads: int, scale: float, window: int | None = None, slopes: torch.Tensor | None = None,
-                   key_part: int = 0, keys1: int | None = None, k1_token: int = 0, fresh_d0: int = 0, want_stats: bool = False):
+                   key_part: int = 0, keys1: int | None = None, k1_token: int = 0, fresh_d0: int = 0, want_stats: bool = False,
+                   leave_parts: bool = False):
     """Attention in its general form: queries ``q0 [N, H, d0]`` and optionally ``q1 [N, H, d1]`` (lanes behind q0's),
     keys and values addressed by ``(page, head, token)`` strides in elements, an optional bias ``-slopes[h] * distance``.
     Returns ``[N, H, value_dim]``.
@@ -988,7 +990,9 @@ def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, p
     ``key_part`` (bfloat16 on the tensor cores only): 1 = only the keys cached before this step; 2 = only the step's own
     tokens, whose keys and values lie token by token (``keys`` lanes ``[0, fresh_d0)`` per head, ``keys1`` the lanes
     behind them, one row a token for all heads).  With ``want_stats`` the result is ``(out, stats [N, H, 2])``: each row's
-    maximum score and sum of exponentials (a row without keys: ``-inf, 0``, and an output that is not to be read), for :func:`merge_two_parts`."""
+    maximum score and sum of exponentials (a row without keys: ``-inf, 0``, and an output that is not to be read), for :func:`merge_two_parts`.
+    ``leave_parts``: where the keys are cut over several CTAs the partial results are not merged but returned as an
+    :class:`AttentionParts`, for a kernel that merges them on its way (:func:`merge_project_gate`)."""
     n, d0 = q0.shape[0], q0.shape[2]
     d1 = 0 if q1 is None else q1.shape[2]
     _need(q0.stride(2) == 1 and (q1 is None or q1.stride(2) == 1), "attention_rows: queries need unit inner strides")
@@ -1013,14 +1017,17 @@ def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, p
             part_ml = torch.empty((n * num_heads * splits * 2,), dtype=torch.float32, device=q0.device)
         code = _launch(
             "llm_attention_rows_mma", _ptr(q0), q0.stride(0), q0.stride(1), d0, _ptr(q1), 0 if q1 is None else q1.stride(0),
-            0 if q1 is None else q1.stride(1), d1, _ptr(out), out.stride(0), out.stride(1), keys, *k_strides, values, *v_strides,
+            0 if q1 is None else q1.stride(1), d1, None if (leave_parts and splits > 1) else _ptr(out), out.stride(0), out.stride(1),
+            keys, *k_strides, values, *v_strides,
             value_dim, _ptr(page_table), page_table.shape[1], _ptr(ctx.token_request), _ptr(ctx.cu_tokens), _ptr(ctx.context_lens),
             _ptr(slopes), n, ctx.num_requests, ctx.max_query_len, num_heads, num_kv_heads, page_size, int(window or 0), float(scale),
             splits, _ptr(part_o), _ptr(part_ml), int(key_part), keys1, int(k1_token), int(fresh_d0), _ptr(stats), _stream(),
         )
         if code != 10002:
-            add_launches(int(splits > 1))
             _check(code, "attention_rows (tensor cores)")
+            if leave_parts and splits > 1:
+                return AttentionParts(part_o, part_ml, splits, n, num_heads, value_dim)
+            add_launches(int(splits > 1))
             return (out, stats) if want_stats else out
         add_launches(-1)  # a layout the kernel does not take: the general one below
     _need(not key_part and not want_stats, "attention over a part of the keys runs on the tensor cores only (bfloat16, lanes in multiples of 16)")
@@ -1031,6 +1038,29 @@ def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, p
         _ptr(ctx.context_lens), _ptr(slopes), n, num_heads, num_kv_heads, page_size, int(window or 0), float(scale), _stream(),
     )
     _check(code, "attention_rows")
+    return out
+
+
+class AttentionParts:
+    """Partial results of attention whose keys were cut over ``splits`` CTAs: ``part_o [n * heads * splits * dv]``
+    unnormalised outputs, ``part_ml [n * heads * splits * 2]`` each part's maximum and sum."""
+
+    def __init__(self, part_o, part_ml, splits: int, n: int, heads: int, dv: int):
+        self.part_o, self.part_ml, self.splits, self.n, self.heads, self.dv = part_o, part_ml, splits, n, heads, dv
+
+
+def merge_project_gate(parts: AttentionParts, w: torch.Tensor, gate: torch.Tensor | None) -> torch.Tensor:
+    """``out[t, h * M + e] = sigmoid(gate[t, h * M + e]) * sum_r w[h, e, r] * merged[t, h, r]`` where ``merged`` is what
+    :class:`AttentionParts` merge to: the merge, the product per head with ``w [heads, M, dv]`` (bfloat16) and the gate
+    (None: none) in one kernel, for steps of few rows."""
+    _need(w.dtype == torch.bfloat16 and w.is_contiguous() and w.dim() == 3 and w.shape[0] == parts.heads and w.shape[2] == parts.dv, "merge_project_gate: w [heads, M, dv] bfloat16")
+    m = w.shape[1]
+    if gate is not None:
+        _need(gate.dtype == torch.bfloat16 and gate.stride(1) == 1 and tuple(gate.shape) == (parts.n, parts.heads * m), "merge_project_gate: gate [n, heads * M] bfloat16")
+    out = torch.empty((parts.n, parts.heads * m), dtype=torch.bfloat16, device=w.device)
+    code = _launch("llm_merge_project_gate", _ptr(parts.part_o), _ptr(parts.part_ml), parts.splits, _ptr(w), _ptr(gate),
+                   0 if gate is None else gate.stride(0), _ptr(out), parts.n, parts.heads, parts.dv, m, _stream())
+    _check(code, "merge_project_gate")
     return out
 
 
@@ -1058,7 +1088,7 @@ def latent_two_parts(ctx, dtype: torch.dtype, *lanes: int) -> bool:
 
 
 def latent_paged_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, plane: torch.Tensor, page_table: torch.Tensor, ctx, *,
-                           rank: int, scale: float, window: int | None = None, cached_only: bool = False):
+                           rank: int, scale: float, window: int | None = None, cached_only: bool = False, leave_parts: bool = False):
     """Attention of every new token over its request's cached latents.  A cached row ``[rank | rot]`` is the key of
     every head (against the query ``[q_lat | q_rot]``) and, in its first ``rank`` lanes, the value.
     ``plane [pages, page_size, rank + rot]``; returns ``[N, H, rank]``.  ``cached_only``: only the rows cached before
@@ -1069,7 +1099,7 @@ def latent_paged_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, plane: torc
     strides = (page_size * width, 0, width)
     return attention_rows(q_lat, q_rot, _ptr(plane), strides, _ptr(plane), strides, rank, page_table, page_size, ctx,
                           num_heads=q_lat.shape[1], num_kv_heads=1, scale=scale, window=window,
-                          key_part=1 if cached_only else 0, want_stats=cached_only)
+                          key_part=1 if cached_only else 0, want_stats=cached_only, leave_parts=leave_parts and not cached_only)
 
 
 def fresh_latent_attention(q_plain: torch.Tensor, q_rot: torch.Tensor, kv: torch.Tensor, fresh: torch.Tensor, page_table: torch.Tensor,

@@ -13,7 +13,8 @@ before it is cached; rotary positions use the interleaved layout (lanes 2i and 2
 computed in 32-bit from the position.  In a bfloat16 step in which a request brings many tokens the softmax is taken in
 two parts that a last kernel joins: the rows cached before the step as above, and the step's own tokens with keys and
 values per head (``W_uk c``, ``W_uv c``: one product for all new tokens), which takes a third of the arithmetic of
-attention over the latents.  The concatenated heads are multiplied by ``sigmoid(W_g x)`` before the output
+attention over the latents; a step whose requests all start at position 0 (``ctx.fresh_requests``) has no cached rows and
+runs the second part alone.  The concatenated heads are multiplied by ``sigmoid(W_g x)`` before the output
 projection.  Sizes, the softmax scale, the rotary base and the names of the tensors are parameters.
 """
 
@@ -101,26 +102,39 @@ class LatentAttention(Mixer):
         )
         q_rot, fresh = prepared if two_parts else (prepared, None)
         q_plain = proj.as_strided((proj.shape[0], H, dim), (proj.stride(0), dim + rot, 1), proj.storage_offset())
-        q_lat = ops.head_linear(q_plain, self.w_uk_t)  # [N, H, rank]
         if two_parts:
-            cached, cached_stats = ops.latent_paged_attention(
-                q_lat, q_rot, cache.pool, cache.page_table, ctx, rank=rank, scale=self.scale, window=self.window, cached_only=True
-            )
             kv = ops.linear(fresh[:, :rank], self.w_up)  # keys and values of the step's own tokens, head by head
             own, own_stats = ops.fresh_latent_attention(
                 q_plain, q_rot, kv, fresh, cache.page_table, ctx, dim=dim, value_dim=self.value_dim, rank=rank, scale=self.scale,
                 window=self.window,
             )
-            heads = ops.merge_two_parts(own, own_stats, ops.head_linear(cached, self.w_uv), cached_stats)
+            if getattr(ctx, "fresh_requests", False):
+                heads = own  # every request starts with this step: there are no cached rows to attend to
+            else:
+                q_lat = ops.head_linear(q_plain, self.w_uk_t)  # [N, H, rank]
+                cached, cached_stats = ops.latent_paged_attention(
+                    q_lat, q_rot, cache.pool, cache.page_table, ctx, rank=rank, scale=self.scale, window=self.window, cached_only=True
+                )
+                heads = ops.merge_two_parts(own, own_stats, ops.head_linear(cached, self.w_uv), cached_stats)
         else:
+            q_lat = ops.head_linear(q_plain, self.w_uk_t)  # [N, H, rank]
             mixed = ops.latent_paged_attention(
-                q_lat, q_rot, cache.pool, cache.page_table, ctx, rank=rank, scale=self.scale, window=self.window
+                q_lat, q_rot, cache.pool, cache.page_table, ctx, rank=rank, scale=self.scale, window=self.window,
+                leave_parts=ctx.num_tokens <= 16,
             )
+            if isinstance(mixed, ops.AttentionParts):
+                # few rows, keys cut over several CTAs: their merge, W_uv and the gate are one kernel
+                gate = proj[:, H * (dim + rot) + rank + rot :] if self.output_gate else None
+                out = ops.merge_project_gate(mixed, self.w_uv, gate)
+                return self._project_out(out, sink)
             heads = ops.head_linear(mixed, self.w_uv)  # [N, H, vdim]
         if self.output_gate:
             out = ops.gate_mul(heads, proj[:, H * (dim + rot) + rank + rot :], "sigmoid")
         else:
             out = heads.reshape(proj.shape[0], H * self.value_dim)
+        return self._project_out(out, sink)
+
+    def _project_out(self, out, sink):
         if sink is not None:
             handed_on = sink.linear(out, self.w_out)
             if handed_on is not None:

@@ -262,7 +262,7 @@ def _attend(q, k, v, first_pos, scale, window, slopes):
     return torch.einsum("htj,jhd->thd", torch.softmax(s, dim=-1), v)
 
 
-def latent_paged_attention(q_lat, q_rot, plane, page_table, ctx, *, rank, scale, window=None):
+def latent_paged_attention(q_lat, q_rot, plane, page_table, ctx, *, rank, scale, window=None, leave_parts=False):
     page_size = plane.shape[1]
     n_tok, heads = q_lat.shape[0], q_lat.shape[1]
     out = torch.empty((n_tok, heads, rank), dtype=q_lat.dtype, device=q_lat.device)

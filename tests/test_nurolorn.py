@@ -329,8 +329,10 @@ def test_long_portions(dtype, engine):
     d.got.clear()
     d.run([("r1", reqs["r1"][:39])])
     d.run([("r0", reqs["r0"][:150]), ("r1", reqs["r1"][39:])], end=["r1"])
-    d.run([("r0", reqs["r0"][150:])], end=["r0"])
-    check(d.got, exp, dtype, "two long portions")
+    d.run([("r0", reqs["r0"][150:320])])
+    for i in range(320, 330):  # decoded over a cache of 320 rows: the keys are cut over several CTAs and merged on the way
+        d.run([("r0", [reqs["r0"][i]])], end=["r0"] if i == 329 else [])
+    check(d.got, exp, dtype, "two long portions, then single tokens")
 
 
 # --------------------------------------------------------------------------------------------- the replay program

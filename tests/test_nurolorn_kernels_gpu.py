@@ -208,7 +208,17 @@ def test_keys_cut_over_several_ctas_are_merged(ops, dtype):
     plane = rnd(num_pages, page_size, rank + rot, dtype=dtype, seed=1)
     q_lat, q_rot = rnd(2, heads, rank, dtype=dtype, seed=2, scale=0.2), rnd(2, heads, rot, dtype=dtype, seed=3, scale=0.2)
     got = ops.latent_paged_attention(q_lat, q_rot, plane, table, ctx, rank=rank, scale=0.5)
-    close(got, plain_ops.latent_paged_attention(q_lat, q_rot, plane, table, ctx, rank=rank, scale=0.5), dtype, "split keys")
+    want = plain_ops.latent_paged_attention(q_lat, q_rot, plane, table, ctx, rank=rank, scale=0.5)
+    close(got, want, dtype, "split keys")
+    if dtype == torch.bfloat16:
+        # the same with the merge, a product per head and a sigmoid gate done by one kernel
+        parts = ops.latent_paged_attention(q_lat, q_rot, plane, table, ctx, rank=rank, scale=0.5, leave_parts=True)
+        assert isinstance(parts, ops.AttentionParts) and parts.splits > 1
+        w = rnd(heads, 24, rank, dtype=dtype, seed=4, scale=0.2)
+        gate = rnd(2, heads * 24 + 8, dtype=dtype, seed=5)[:, 8:]
+        ref = plain_ops.gate_mul(plain_ops.head_linear(want, w), gate, "sigmoid")
+        close(ops.merge_project_gate(parts, w, gate), ref, dtype, "merge, product per head and gate in one")
+        close(ops.merge_project_gate(parts, w, None), plain_ops.head_linear(want, w).reshape(2, -1), dtype, "without a gate")
 
 
 def one_hot_case(ops, dtype, generic, monkeypatch, *, form, context, query_len, target_distance, window, page_size=16):
