@@ -446,7 +446,7 @@ LLM_EXPORT int llm_attention_rows_mma(const void* q0, long long q0_token, long l
     const int dk = d0 + d1;
     auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
     if ((d0 & 15) || (d1 & 15) || (dv & 15) || dv > 256 || dk > 640) return LLM_ERR_UNSUPPORTED;
-    if (key_part < 0 || key_part > 2 || ((key_part != 0 || stats) && splits != 1)) return LLM_ERR_BAD_ARGUMENT;
+    if (key_part < 0 || key_part > 2 || (stats && splits != 1)) return LLM_ERR_BAD_ARGUMENT;
     if (key_part == 2 && keys1 && ((fresh_d0 & 15) || fresh_d0 <= 0 || fresh_d0 >= dk || (k1_token & 7) || ((uintptr_t)keys1 & 15)))
         return LLM_ERR_UNSUPPORTED;
     if ((q0_token & 7) || (q0_head & 7) || (q1_token & 7) || (q1_head & 7) || (k_page & 7) || (k_head & 7) || (k_token & 7) ||
@@ -474,7 +474,7 @@ LLM_EXPORT int llm_attention_rows_mma(const void* q0, long long q0_token, long l
     if (smem > 220 * 1024) return LLM_ERR_UNSUPPORTED;
     int code;
     // many rows per key/value head (long prompt portions), values of at most 128 lanes: 128 rows a CTA
-    const bool tall = wide && splits == 1 && dv <= 128 && (long long)max_query_len * (H / KV) >= 512 && smem_for(64, 128) <= 100 * 1024;
+    const bool tall = wide && dv <= 128 && (long long)max_query_len * (H / KV) >= 512 && smem_for(64, 128) <= 100 * 1024;
     if (tall) {
         smem = smem_for(64, 128);
         code = dv <= 64 ? launch<64, 64, 128>(a, requests, max_query_len, splits, part_o, part_ml, smem, stream)

@@ -1103,10 +1103,11 @@ def latent_paged_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, plane: torc
 
 
 def fresh_latent_attention(q_plain: torch.Tensor, q_rot: torch.Tensor, kv: torch.Tensor, fresh: torch.Tensor, page_table: torch.Tensor,
-                           ctx, *, dim: int, value_dim: int, rank: int, scale: float, window: int | None = None):
+                           ctx, *, dim: int, value_dim: int, rank: int, scale: float, window: int | None = None, want_stats: bool = True):
     """Attention of every new token over the step's own tokens of its request, with keys and values per head:
     ``kv [N, H * dim | H * value_dim]`` (the latents' products with the two up matrices), the rotated shared key part in
-    ``fresh[:, rank:]``.  Returns ``(out [N, H, value_dim], stats)`` for :func:`merge_two_parts`."""
+    ``fresh[:, rank:]``.  Returns ``(out [N, H, value_dim], stats)`` for :func:`merge_two_parts`, or ``out`` alone
+    without ``want_stats``."""
     n, heads = q_plain.shape[0], q_plain.shape[1]
     rot = fresh.shape[1] - rank
     _need(kv.is_contiguous() and fresh.is_contiguous() and kv.shape[1] == heads * (dim + value_dim), "fresh_latent_attention: kv [N, H dim | H vdim]")
@@ -1114,7 +1115,7 @@ def fresh_latent_attention(q_plain: torch.Tensor, q_rot: torch.Tensor, kv: torch
     return attention_rows(q_plain, q_rot, kv.data_ptr(), (0, dim, kv.stride(0)), kv.data_ptr() + heads * dim * element,
                           (0, value_dim, kv.stride(0)), value_dim, page_table, 1, ctx, num_heads=heads, num_kv_heads=heads,
                           scale=scale, window=window, key_part=2, keys1=fresh.data_ptr() + rank * element, k1_token=rank + rot,
-                          fresh_d0=dim, want_stats=True)
+                          fresh_d0=dim, want_stats=want_stats)
 
 
 def biased_paged_attention(qkv: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor, ctx, *, num_heads: int, num_kv_heads: int,

@@ -104,13 +104,15 @@ class LatentAttention(Mixer):
         q_plain = proj.as_strided((proj.shape[0], H, dim), (proj.stride(0), dim + rot, 1), proj.storage_offset())
         if two_parts:
             kv = ops.linear(fresh[:, :rank], self.w_up)  # keys and values of the step's own tokens, head by head
-            own, own_stats = ops.fresh_latent_attention(
+            alone = bool(getattr(ctx, "fresh_requests", False))  # every request starts with this step: no cached rows
+            own = ops.fresh_latent_attention(
                 q_plain, q_rot, kv, fresh, cache.page_table, ctx, dim=dim, value_dim=self.value_dim, rank=rank, scale=self.scale,
-                window=self.window,
+                window=self.window, want_stats=not alone,
             )
-            if getattr(ctx, "fresh_requests", False):
-                heads = own  # every request starts with this step: there are no cached rows to attend to
+            if alone:
+                heads = own
             else:
+                own, own_stats = own
                 q_lat = ops.head_linear(q_plain, self.w_uk_t)  # [N, H, rank]
                 cached, cached_stats = ops.latent_paged_attention(
                     q_lat, q_rot, cache.pool, cache.page_table, ctx, rank=rank, scale=self.scale, window=self.window, cached_only=True
