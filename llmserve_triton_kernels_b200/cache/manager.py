@@ -23,7 +23,7 @@ from dataclasses import dataclass
 import numpy as np
 import torch
 
-from ..parts.base import PagedKVSpec, PagedRowSpec, StateSpec
+from ..parts.base import CompositeSpec, PagedKVSpec, PagedRowSpec, StateSpec
 from .allocator import IdAllocator, OutOfPages
 
 RELEASED = -1  # table entry of a page that a window has passed
@@ -47,6 +47,22 @@ class StateView:
     states: torch.Tensor  # [slots, *shape]
     slots: torch.Tensor  # [requests] int32 (device)
     host_slots: list[int]
+
+
+@dataclass
+class CompositeView:
+    """What a mixer made of several sees: one view per part, in the order of its ``CompositeSpec``."""
+
+    parts: list
+
+
+def leaf_views(view):
+    """The views of one entry of the order that hold something: the view itself, or a composite's parts."""
+    if isinstance(view, CompositeView):
+        for part in view.parts:
+            yield from leaf_views(part)
+    elif view is not None:
+        yield view
 
 
 class PageGroup:
@@ -129,18 +145,29 @@ class CacheManager:
         self.dtype = dtype
         self.schedule = list(schedule)
         self.groups: list[PageGroup] = []
-        self._entry_group: dict[int, tuple[int, int]] = {}  # order entry -> (group, plane)
+        self._entry_group: dict[object, tuple[int, int]] = {}  # order entry (or (entry, part)) -> (group, plane)
         by_spec: dict[PagedKVSpec | PagedRowSpec, list[int]] = {}
-        self._state_entries: dict[int, torch.Tensor] = {}
-        for i, spec in enumerate(cache_specs):
+        self._state_entries: dict[object, torch.Tensor] = {}
+        self._composites: dict[int, int] = {}  # order entry -> how many parts its mixer keeps things for
+
+        def take(key, spec):
+            """``key``: an entry of the order, or ``(entry, part)`` for a part of a composite."""
             if isinstance(spec, (PagedKVSpec, PagedRowSpec)):
-                by_spec.setdefault(spec, []).append(i)
+                by_spec.setdefault(spec, []).append(key)
             elif isinstance(spec, StateSpec):
-                self._state_entries[i] = torch.zeros(
+                self._state_entries[key] = torch.zeros(
                     (self.max_requests, *spec.shape), dtype=spec.dtype, device=self.device
                 )
             elif spec is not None:
-                raise TypeError(f"entry {i} of the order has an unknown cache spec {spec!r}")
+                raise TypeError(f"entry {key} of the order has an unknown cache spec {spec!r}")
+
+        for i, spec in enumerate(cache_specs):
+            if isinstance(spec, CompositeSpec):
+                self._composites[i] = len(spec.parts)
+                for j, part in enumerate(spec.parts):
+                    take((i, j), part)
+            else:
+                take(i, spec)
         for g, (spec, entries) in enumerate(by_spec.items()):
             self.groups.append(PageGroup(spec, entries, self.num_pages, self.page_size, dtype, self.device))
             for plane, i in enumerate(entries):
@@ -294,16 +321,22 @@ class CacheManager:
 
     def views(self, group_tensors, state_slots: torch.Tensor, host_slots: list[int]) -> list:
         """One view per entry of the order, from the device copies of ``step_tables``'s arrays."""
+
+        def view(key):
+            if key in self._entry_group:
+                g, plane = self._entry_group[key]
+                group = self.groups[g]
+                table, slot_map = group_tensors[g]
+                return PagedKVView(group.pool[plane], table, slot_map, group.page_size, group.spec)
+            if key in self._state_entries:
+                return StateView(self._state_entries[key], state_slots, host_slots)
+            return None
+
         views: list = []
         for i, run in enumerate(self.schedule):
             src = i if run.cache_of is None else run.cache_of
-            if src in self._entry_group:
-                g, plane = self._entry_group[src]
-                group = self.groups[g]
-                table, slot_map = group_tensors[g]
-                views.append(PagedKVView(group.pool[plane], table, slot_map, group.page_size, group.spec))
-            elif src in self._state_entries:
-                views.append(StateView(self._state_entries[src], state_slots, host_slots))
+            if src in self._composites:
+                views.append(CompositeView([view((src, j)) for j in range(self._composites[src])]))
             else:
-                views.append(None)
+                views.append(view(src))
         return views

@@ -1,5 +1,6 @@
 from .llama import ConfigError, LlamaConfig  # noqa: F401
 from .nurolorn import NurolornConfig  # noqa: F401
+from .kafepel import KafepelConfig  # noqa: F401
 from .registry import (  # noqa: F401
     Architecture,
     architecture_of,

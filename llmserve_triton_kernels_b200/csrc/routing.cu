@@ -1,0 +1,152 @@
+// A router that picks a few of many small feed-forward layers per token, the step that applies its weights, and
+// the meeting of mixers that run side by side.
+//
+// The router's scores, the choice and the weights are 32-bit.
+#include "common.cuh"
+
+#include <float.h>
+
+namespace {
+
+// One warp per token.  z: [N, ldz] float32 router logits (the first E of a row; column E, if there is a shared gate,
+// holds its logit).
+//   s = softmax(z[0:E]);   chosen = the `top` experts with the largest s + correction (lowest index among equals)
+//   w[t, e] = scale * s[e] (divided by the chosen scores' sum if renorm) for chosen experts, 0 for the others
+//   w[t, E] = sigmoid(z[t, E]) if shared_gate
+// w: [N, E + shared_gate] float32
+__global__ void __launch_bounds__(128)
+route_topk_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ correction, float* __restrict__ w, int N, int E,
+                  int top, float scale, int renorm, int shared_gate) {
+    extern __shared__ float sm[];  // per warp: s[E], choice[E]
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    float* s = sm + (size_t)warp * 2 * E;
+    float* c = s + E;
+    pdl_wait();
+    if (t >= N) return;
+    const float* zr = z + (size_t)t * ldz;
+    float* wr = w + (size_t)t * (E + shared_gate);
+    float m = -FLT_MAX;
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, zr[e]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+        const float x = expf(zr[e] - m);
+        s[e] = x;
+        sum += x;
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+    for (int e = lane; e < E; e += 32) {
+        s[e] *= inv;
+        c[e] = s[e] + (correction ? correction[e] : 0.f);
+        wr[e] = 0.f;
+    }
+    __syncwarp();
+    float chosen_sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float best = -FLT_MAX;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < E; e += 32)
+            if (c[e] > best) { best = c[e]; arg = e; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (arg < E) {
+            if (lane == 0) {
+                c[arg] = -FLT_MAX;
+                wr[arg] = -1.f;  // marked; its weight follows
+            }
+            chosen_sum += s[arg];
+        }
+        __syncwarp();
+    }
+    const float f = renorm ? scale / chosen_sum : scale;
+    for (int e = lane; e < E; e += 32)
+        if (wr[e] < 0.f) wr[e] = s[e] * f;
+    if (shared_gate && lane == 0) wr[E] = 1.f / (1.f + expf(-zr[E]));
+}
+
+__device__ __forceinline__ float activate(float v, int kind) {
+    if (kind == 0) { const float r = fmaxf(v, 0.f); return r * r; }                                                // relu^2
+    if (kind == 1) return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));              // gelu (tanh)
+    if (kind == 3) return v / (1.f + expf(-v));                                                                    // silu
+    return v;
+}
+
+// y[t, j] = act(x[t, j]) * w[t, block(j)]: block(j) = j / ff for j < E * ff, and E for the columns behind them (a
+// shared expert's).  x, y: [N, C].
+template <typename T>
+__global__ void __launch_bounds__(256)
+expert_act_scale_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w, int ldw, T* __restrict__ y, int ldy, int N, int C,
+                        int E, int ff, int kind) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.y;
+    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < C; j += gridDim.x * blockDim.x) {
+        const int b = j < E * ff ? j / ff : E;
+        const float wt = w[(size_t)t * ldw + b];
+        y[(size_t)t * ldy + j] = from_float<T>(wt == 0.f ? 0.f : activate(to_float(x[(size_t)t * ldx + j]), kind) * wt);
+    }
+}
+
+// out[t, :] = factor * sum_b  x_b[t, :] / sqrt(mean(x_b[t, :]^2) + eps) * w_b        (b < count <= 4), one CTA per row
+struct Branches {
+    const float* x[4];
+    const float* w[4];
+};
+
+__global__ void __launch_bounds__(256)
+branch_norm_sum_kernel(Branches br, int count, float* __restrict__ out, int C, float eps, float factor) {
+    __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
+    const size_t row = (size_t)blockIdx.x * C;
+    float scale[4];
+    for (int b = 0; b < count; ++b) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < C; i += blockDim.x) { const float v = br.x[b][row + i]; ss = fmaf(v, v, ss); }
+        ss = block_sum(ss, scratch);
+        scale[b] = 1.f / sqrtf(ss / (float)C + eps);
+    }
+    for (int i = threadIdx.x; i < C; i += blockDim.x) {
+        float s = 0.f;
+        for (int b = 0; b < count; ++b) s += br.x[b][row + i] * scale[b] * br.w[b][i];
+        out[row + i] = s * factor;
+    }
+}
+
+}  // namespace
+
+LLM_EXPORT int llm_route_topk(const float* z, int ldz, const float* correction, float* w, int N, int E, int top, float scale,
+                              int renorm, int shared_gate, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (E <= 0 || top < 1 || top > E || E > 4096 || ldz < E + (shared_gate ? 1 : 0)) return LLM_ERR_BAD_ARGUMENT;
+    const size_t smem = (size_t)4 * 2 * E * sizeof(float);
+    return launch_pdl(route_topk_kernel, dim3((N + 3) / 4), dim3(128), smem, stream, z, ldz, correction, w, N, E, top, scale, renorm,
+                      shared_gate ? 1 : 0);
+}
+
+LLM_EXPORT int llm_expert_act_scale(const void* x, int ldx, const float* w, int ldw, void* y, int ldy, int dtype, int N, int C, int E,
+                                    int ff, int kind, cudaStream_t stream) {
+    if (N <= 0 || C <= 0) return 0;
+    if (E < 0 || ff <= 0 || (size_t)E * ff > (size_t)C || N > 65535) return LLM_ERR_BAD_ARGUMENT;
+    const dim3 grid((C + 255) / 256 < 64 ? (C + 255) / 256 : 64, N), block(256);
+    if (dtype == LLM_F32)
+        return launch_pdl(expert_act_scale_kernel<float>, grid, block, 0, stream, (const float*)x, ldx, w, ldw, (float*)y, ldy, N, C, E, ff, kind);
+    return launch_pdl(expert_act_scale_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)x, ldx, w, ldw,
+                      (__nv_bfloat16*)y, ldy, N, C, E, ff, kind);
+}
+
+LLM_EXPORT int llm_branch_norm_sum(const float* x0, const float* w0, const float* x1, const float* w1, const float* x2, const float* w2,
+                                   const float* x3, const float* w3, int count, float* out, int N, int C, float eps, float factor,
+                                   cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (count < 1 || count > 4 || C <= 0) return LLM_ERR_BAD_ARGUMENT;
+    Branches br = {{x0, x1, x2, x3}, {w0, w1, w2, w3}};
+    return launch_pdl(branch_norm_sum_kernel, dim3(N), dim3(256), 0, stream, br, count, out, C, eps, factor);
+}

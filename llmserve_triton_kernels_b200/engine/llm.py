@@ -22,7 +22,7 @@ from ..cache import CacheManager, num_pages_for_budget
 from ..config.presets import PRESETS
 from ..config.registry import architecture_of
 from ..models.load import load_model, random_model, resolve_dtype
-from ..parts.base import PagedKVSpec, PagedRowSpec
+from ..parts.base import PagedKVSpec, PagedRowSpec, flat_specs
 from ..sampling import Sampler, SamplingParams
 from .scheduler import Scheduler
 from .step import StepFunction
@@ -96,7 +96,7 @@ class LLM:
                 cap = want
                 if self.device.type == "cuda":
                     free, _ = torch.cuda.mem_get_info(self.device)
-                    groups = {s for s in specs if isinstance(s, (PagedKVSpec, PagedRowSpec))}
+                    groups = {s for s in flat_specs(specs) if isinstance(s, (PagedKVSpec, PagedRowSpec))}
                     cap = num_pages_for_budget(specs, block_size, element, free // 4) // max(1, len(groups))
                 num_blocks = max(1, min(want, cap))
         self.cache = CacheManager(

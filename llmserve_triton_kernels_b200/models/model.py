@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from ..parts.base import Block, PagedKVSpec, PagedRowSpec, StateSpec, TensorSpec, build_part, part_factory
+from ..parts.base import Block, CompositeSpec, PagedKVSpec, PagedRowSpec, StateSpec, TensorSpec, build_part, part_factory
 from .plan import ModelPlan
 
 
@@ -110,7 +110,7 @@ class Model:
         ) and getattr(self.final_norm, "graph_safe", False)
 
     # ------------------------------------------------------------------ caches
-    def cache_specs(self) -> list[PagedKVSpec | PagedRowSpec | StateSpec | None]:
+    def cache_specs(self) -> list[PagedKVSpec | PagedRowSpec | StateSpec | CompositeSpec | None]:
         """For each entry of the order: what its mixer keeps, or None if it keeps nothing of its
         own (no cache, or it reads an earlier entry's)."""
         out = []
@@ -159,6 +159,9 @@ class Model:
 
     def _check_step(self, ctx, caches) -> None:
         """Checked mode: the step's arrays are looked over on the device before any kernel indexes with them."""
+        from ..cache.manager import leaf_views
+
+        caches = [leaf for c in caches for leaf in leaf_views(c)]
         slots = next((c.states.shape[0] for c in caches if hasattr(c, "states")), 0)
         ops.check_step_arrays(ctx, self.plan.vocab_size, self.plan.max_positions or 0x7FFFFFFF, slots)
         seen = []
@@ -171,7 +174,10 @@ class Model:
         """The residual stream that the first layer meets: the tokens' rows of the table, in 32-bit ``[N, hidden]``.
         An architecture that scales or otherwise prepares its embeddings overrides this in a subclass that it names
         when it registers (``register_architecture(..., model_class=...)``)."""
-        return ops.embed(ctx.token_ids, self.embedding)
+        x = ops.embed(ctx.token_ids, self.embedding)
+        if self.plan.embedding_scale != 1.0:
+            ops.unary(x, "scale", self.plan.embedding_scale, inplace=True)
+        return x
 
     def project_logits(self, x) -> torch.Tensor:
         """32-bit logits ``[rows, vocab]`` of the normalised rows ``x`` (a tensor, or the factored form that the

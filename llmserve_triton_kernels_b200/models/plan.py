@@ -84,6 +84,7 @@ class ModelPlan:
     injections: tuple[Injection, ...] = ()
     extra_tensors: tuple[tuple[str, tuple[int, ...]], ...] = ()  # (name, shape) of tensors that belong to no part
     logit_scale: float = 1.0  # the logits are the output matrix's product times this
+    embedding_scale: float = 1.0  # the residual stream starts as the tokens' rows of the table times this
 
     def __post_init__(self) -> None:
         for i, run in enumerate(self.schedule):

@@ -57,6 +57,14 @@ _SIGNATURES = {
                                _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp, _i, _vp, _ll, _i, _vp, _vp],
     "llm_gemm_simt_batched": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _vp],
     "llm_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    "llm_sigmoid_attention": [_vp, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i,
+                              _i, _i, _vp],
+    "llm_qk_prepare": [_vp, _i, _i, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _f, _vp, _i, _vp, _f, _i, _i, _i, _i, _i, _vp],
+    "llm_retention_scan": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "llm_head_norm_gate": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _i, _vp],
+    "llm_route_topk": [_vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp],
+    "llm_expert_act_scale": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "llm_branch_norm_sum": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _f, _f, _vp],
 }
 
 
@@ -1134,3 +1142,160 @@ def biased_paged_attention(qkv: torch.Tensor, pool: torch.Tensor, page_table: to
     out = attention_rows(q, None, _ptr(pool), (page, head, row), values, (page, head, row), value_dim, page_table, page_size, ctx,
                          num_heads=num_heads, num_kv_heads=num_kv_heads, scale=scale, window=window, slopes=slopes)
     return out.view(qkv.shape[0], num_heads * value_dim)
+
+
+# ------------------------------------------------------------------------------------------------
+# Operations of layers whose attention weighs keys by a sigmoid and mixes the heads' weights, that keep a decaying
+# matrix of state per head, that route tokens to a few of many small feed-forward layers, or that run mixers side by
+# side (csrc/sigmoid_attention.cu, retention.cu, routing.cu).
+_SIGMOID_SPLIT_KEYS = 256  # a stretch of keys that one CTA sums up when a context is shared out
+_SIGMOID_SPLIT_MAX_TOKENS = 64  # steps of more tokens have CTAs enough without cutting the keys
+
+
+def qk_prepare(proj: torch.Tensor, positions: torch.Tensor | None, *, heads: int, kv_heads: int, dim: int, value_dim: int = 0,
+               freq: torch.Tensor | None = None, q_weight: torch.Tensor | None = None, k_weight: torch.Tensor | None = None,
+               eps: float = 0.0, k_scale: float = 1.0, pool: torch.Tensor | None = None, slot_map: torch.Tensor | None = None,
+               out_dtype: torch.dtype | None = None):
+    """From a token's stacked projections ``proj`` rows ``[heads x dim | kv_heads x dim | kv_heads x value_dim | ...]``
+    to queries and keys: with ``q_weight`` / ``k_weight`` (float32, the whole projection's size) the query projection and
+    the key projection are each RMS-normed as one vector (``eps`` inside the root) and weighted; with ``freq``
+    (float32 ``[rot / 2]``) lanes ``i`` and ``i + rot/2`` of every head turn by ``position * freq[i]`` (32-bit angles);
+    keys are multiplied by ``k_scale``.  With ``pool [pages, 2, kv_heads, page_size, D]`` keys and values go to the
+    tokens' slots and the queries ``[N, heads * dim]`` (``out_dtype``, default the pool's type) are returned; without,
+    ``(queries, keys [N, kv_heads * dim])`` in ``out_dtype`` are."""
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] >= (heads + kv_heads) * dim + (kv_heads * value_dim if pool is not None else 0), "qk_prepare: proj rows are too short")
+    n = proj.shape[0]
+    rot = 0
+    if freq is not None:
+        _need(freq.dtype == torch.float32 and freq.is_contiguous(), "qk_prepare: freq is float32")
+        _i32(positions, "positions")
+        rot = 2 * freq.numel()
+    for w, size in ((q_weight, heads * dim), (k_weight, kv_heads * dim)):
+        _need(w is None or (w.dtype == torch.float32 and w.is_contiguous() and w.numel() == size), "qk_prepare: norm weights are float32 of the projection's size")
+    if pool is not None:
+        _need(pool.is_contiguous() and pool.dim() == 5 and tuple(pool.shape[1:3]) == (2, kv_heads), "the pool plane does not match the heads")
+        _i32(slot_map, "slot_map")
+        out_dtype = pool.dtype
+    out_dtype = out_dtype or proj.dtype
+    q = torch.empty((n, heads * dim), dtype=out_dtype, device=proj.device)
+    k = None if pool is not None else torch.empty((n, kv_heads * dim), dtype=out_dtype, device=proj.device)
+    code = _launch(
+        "llm_qk_prepare", _ptr(proj), _code(proj.dtype), proj.stride(0), _ptr(q), _code(out_dtype), q.stride(0), _ptr(k),
+        0 if k is None else k.stride(0), _ptr(pool), _code(out_dtype), _ptr(slot_map), 0 if pool is None else pool.shape[3],
+        0 if pool is None else pool.shape[4], _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(freq), rot, _ptr(positions),
+        float(k_scale), n, heads, kv_heads, dim, value_dim, _stream(),
+    )
+    _check(code, "qk_prepare")
+    return q if pool is not None else (q, k)
+
+
+def sigmoid_attention(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor, ctx, *, num_heads: int, num_kv_heads: int,
+                      key_dim: int, value_dim: int, scale: float, softcap: float | None = None, head_bias: torch.Tensor | None = None,
+                      head_mix: torch.Tensor | None = None, window: int | None = None) -> torch.Tensor:
+    """Attention whose weights are not normalised over keys: key j (``j <= i``, within ``window`` if there is one) gets
+    ``sigmoid(cap(scale * q_g . k_j) + head_bias[g])`` with ``cap(s) = softcap * tanh(s / softcap)``, the heads' weights
+    are mixed (``w_h = sum_g head_mix[h, g] p_g``) and head h sums up the values of its own key/value head with them.
+    ``q [N, heads * key_dim]``; keys and values in ``pool [pages, 2, kv_heads, page_size, D]``.  Returns
+    ``[N, heads * value_dim]``.  A step of few tokens shares long contexts out over several CTAs in stretches of a fixed
+    number of keys and adds the partial sums in order."""
+    _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] == num_heads * key_dim, "sigmoid_attention: q [N, heads * key_dim]")
+    _need(pool.dtype == q.dtype and pool.is_contiguous() and pool.dim() == 5 and tuple(pool.shape[1:3]) == (2, num_kv_heads), "the pool plane does not match the heads")
+    _i32(page_table, "page_table")
+    for name, t, size in (("head_bias", head_bias, num_heads), ("head_mix", head_mix, num_heads * num_heads)):
+        _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == size), f"sigmoid_attention: {name} is float32 of the heads' size")
+    n = q.shape[0]
+    out = torch.empty((n, num_heads * value_dim), dtype=q.dtype, device=q.device)
+    longest = getattr(ctx, "max_context_len", None) or int(ctx.context_lens.max())
+    if window:
+        longest = min(longest, window + ctx.max_query_len)
+    splits = 1 if n > _SIGMOID_SPLIT_MAX_TOKENS else max(1, min(-(-longest // _SIGMOID_SPLIT_KEYS), 1024))
+    parts = torch.empty((splits, n, num_heads * value_dim), dtype=torch.float32, device=q.device) if splits > 1 else None
+    code = _launch(
+        "llm_sigmoid_attention", _ptr(q), _code(q.dtype), q.stride(0), _ptr(pool), _code(pool.dtype), _ptr(page_table),
+        page_table.shape[1], _ptr(ctx.positions), _ptr(ctx.token_request), _ptr(head_bias), _ptr(head_mix), _ptr(out),
+        _code(out.dtype), _ptr(parts), n, num_heads, num_kv_heads, key_dim, value_dim, pool.shape[4], pool.shape[3], float(scale),
+        float(softcap or 0.0), int(window or 0), _SIGMOID_SPLIT_KEYS, splits, _stream(),
+    )
+    _check(code, "sigmoid_attention")
+    add_launches(int(splits > 1))
+    return out
+
+
+def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, states: torch.Tensor,
+                   state_slots: torch.Tensor, cu_tokens: torch.Tensor, num_requests: int, heads: int, dim: int, value_dim: int) -> torch.Tensor:
+    """``S = decay[h] * S + k_t v_t^T``, ``o_t = S^T q_t`` per head over every request's new tokens
+    ``cu_tokens[r]:cu_tokens[r+1]``, from and to ``states[state_slots[r]]`` (``[slots, heads, dim, value_dim]``
+    float32).  ``q, k [N, heads * dim]`` float32, ``v [N, heads * value_dim]`` (a view with a row pitch will do).
+    Returns ``o [N, heads, value_dim]`` float32."""
+    _need(q.dtype == torch.float32 and k.dtype == torch.float32 and q.stride(1) == 1 and k.stride(1) == 1, "retention_scan: queries and keys are float32")
+    _need(v.stride(1) == 1 and v.shape[1] == heads * value_dim, "retention_scan: v [N, heads * value_dim]")
+    _need(states.dtype == torch.float32 and states.is_contiguous() and tuple(states.shape[1:]) == (heads, dim, value_dim), "retention_scan: states [slots, heads, dim, value_dim] float32")
+    _need(decay.dtype == torch.float32 and decay.is_contiguous() and decay.numel() == heads, "retention_scan: decay is float32 [heads]")
+    _i32(state_slots, "state_slots")
+    _i32(cu_tokens, "cu_tokens")
+    out = torch.empty((q.shape[0], heads, value_dim), dtype=torch.float32, device=q.device)
+    code = _launch("llm_retention_scan", _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), _code(v.dtype), v.stride(0), _ptr(decay),
+                   _ptr(states), _ptr(state_slots), _ptr(cu_tokens), _ptr(out), int(num_requests), heads, dim, value_dim, _stream())
+    _check(code, "retention_scan")
+    return out
+
+
+def head_norm_gate(o: torch.Tensor, gate: torch.Tensor | None, eps: float | None, kind: str = "silu",
+                   out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """``o [N, heads, W]`` (float32): every head divided by its root mean square ``sqrt(mean(o^2) + eps)`` (``eps`` None:
+    not), times ``kind`` (``silu`` or ``sigmoid``) of ``gate [N, heads * W]`` (None: no gate) -> ``[N, heads * W]``."""
+    _need(o.dtype == torch.float32 and o.is_contiguous() and o.dim() == 3, "head_norm_gate: o is contiguous float32 [N, heads, W]")
+    n, heads, w = o.shape
+    if gate is not None:
+        _need(gate.stride(1) == 1 and gate.shape[1] == heads * w and kind in _GATE_KINDS, "head_norm_gate: gate [N, heads * W]")
+    out = torch.empty((n, heads * w), dtype=out_dtype, device=o.device)
+    code = _launch("llm_head_norm_gate", _ptr(o), _ptr(gate), _code(gate.dtype) if gate is not None else _code(out_dtype),
+                   0 if gate is None else gate.stride(0), _ptr(out), _code(out_dtype), n, heads, w,
+                   -1.0 if eps is None else float(eps), _GATE_KINDS[kind] if gate is not None else -1, _stream())
+    _check(code, "head_norm_gate")
+    return out
+
+
+def route_topk(z: torch.Tensor, correction: torch.Tensor | None, experts: int, top: int, scale: float = 1.0,
+               renormalize: bool = False, shared_gate: bool = False) -> torch.Tensor:
+    """Router weights of every token as a dense matrix.  ``z [N, >= experts (+ 1)]`` float32 logits; ``s = softmax`` over
+    the first ``experts``; the ``top`` experts with the largest ``s + correction`` are chosen (the lowest index among
+    equals) and get ``scale * s`` (over the chosen ones' sum with ``renormalize``), the others 0.  With ``shared_gate``
+    a last column holds ``sigmoid(z[:, experts])``.  Returns ``[N, experts (+ 1)]`` float32."""
+    _need(z.dtype == torch.float32 and z.dim() == 2 and z.stride(1) == 1, "route_topk: logits are float32")
+    _need(correction is None or (correction.dtype == torch.float32 and correction.is_contiguous() and correction.numel() == experts), "route_topk: correction is float32 [experts]")
+    out = torch.empty((z.shape[0], experts + int(shared_gate)), dtype=torch.float32, device=z.device)
+    code = _launch("llm_route_topk", _ptr(z), z.stride(0), _ptr(correction), _ptr(out), z.shape[0], experts, top, float(scale),
+                   int(renormalize), int(shared_gate), _stream())
+    _check(code, "route_topk")
+    return out
+
+
+def expert_act_scale(x: torch.Tensor, weights: torch.Tensor, experts: int, ff: int, activation: str) -> torch.Tensor:
+    """``act(x[t, j]) * weights[t, j // ff]`` for the first ``experts * ff`` columns, ``* weights[t, experts]`` for
+    the columns behind them (a shared expert's); ``x [N, C]``, ``weights`` float32."""
+    _need(activation in _UNARY_KINDS and x.dim() == 2 and x.stride(1) == 1, f"expert_act_scale: activation {activation!r}")
+    _need(weights.dtype == torch.float32 and weights.stride(1) == 1 and weights.shape[0] == x.shape[0], "expert_act_scale: weights are float32 [N, blocks]")
+    _need(weights.shape[1] >= experts + int(x.shape[1] > experts * ff), "expert_act_scale: a weight per block of columns")
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    code = _launch("llm_expert_act_scale", _ptr(x), x.stride(0), _ptr(weights), weights.stride(0), _ptr(out), out.stride(0),
+                   _code(x.dtype), x.shape[0], x.shape[1], experts, ff, _UNARY_KINDS[activation], _stream())
+    _check(code, "expert_act_scale")
+    return out
+
+
+def branch_norm_sum(branches: list[torch.Tensor], weights: list[torch.Tensor], eps: float, factor: float) -> torch.Tensor:
+    """``factor * sum_b rmsnorm(branches[b]) * weights[b]`` row by row: float32 ``[N, C]`` tensors (up to four), each
+    divided by its own root mean square (``eps`` inside the root)."""
+    _need(1 <= len(branches) <= 4 and len(weights) == len(branches), "branch_norm_sum: one to four branches, a weight each")
+    n, c = branches[0].shape
+    for x, w in zip(branches, weights):
+        _need(x.dtype == torch.float32 and x.is_contiguous() and tuple(x.shape) == (n, c), "branch_norm_sum: branches are contiguous float32 of one shape")
+        _need(w.dtype == torch.float32 and w.is_contiguous() and w.numel() == c, "branch_norm_sum: weights are float32 of the row size")
+    out = torch.empty((n, c), dtype=torch.float32, device=branches[0].device)
+    ptrs = []
+    for i in range(4):
+        ptrs += [_ptr(branches[i]), _ptr(weights[i])] if i < len(branches) else [None, None]
+    code = _launch("llm_branch_norm_sum", *ptrs, len(branches), _ptr(out), n, c, float(eps), float(factor), _stream())
+    _check(code, "branch_norm_sum")
+    return out

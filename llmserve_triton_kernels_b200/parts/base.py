@@ -74,6 +74,23 @@ class StateSpec:
     dtype: torch.dtype = torch.float32
 
 
+@dataclass(frozen=True)
+class CompositeSpec:
+    """A mixer made of several that run side by side, each keeping something of its own (or nothing: None): the cache
+    manager holds every part as it would a layer's, and the mixer sees a ``CompositeView`` with one view per part."""
+
+    parts: tuple
+
+
+def flat_specs(specs):
+    """Every cache spec of a list, the parts of composites in place of the composites."""
+    for spec in specs:
+        if isinstance(spec, CompositeSpec):
+            yield from flat_specs(spec.parts)
+        else:
+            yield spec
+
+
 class Part:
     category = "part"
     # True if forward() launches the same device work for the same shapes whatever the step's
@@ -124,13 +141,13 @@ class PositionEncoding(Part):
 class Mixer(Part):
     category = "mixer"
 
-    def cache_spec(self) -> PagedKVSpec | PagedRowSpec | StateSpec | None:
+    def cache_spec(self) -> PagedKVSpec | PagedRowSpec | StateSpec | CompositeSpec | None:
         return None
 
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         """``x [N, hidden]`` (normalised) -> the mixer's contribution to the residual ``[N, hidden]``.
         ``ctx`` is the step's :class:`StepContext`; ``cache`` what the cache manager holds for this
-        run of the layer (a ``PagedKVView``, a ``StateView`` or None)."""
+        run of the layer (a ``PagedKVView``, a ``StateView``, a ``CompositeView`` or None)."""
         raise NotImplementedError
 
 

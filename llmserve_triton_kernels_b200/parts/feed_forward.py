@@ -18,7 +18,10 @@ _ACTIVATIONS = ("silu",)
 class GatedMLP(FeedForward):
     graph_safe = True
 
-    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu", bias: bool = False):
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu", bias: bool = False,
+                 tensor_names: dict[str, str] | None = None):
+        """``tensor_names``: local names of the three matrices (default ``gate_proj.weight`` and so on)."""
+        self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight", **(tensor_names or {})}
         if activation not in _ACTIVATIONS:
             raise ValueError(f"activation {activation!r} is not built; known: {_ACTIVATIONS}")
         self.hidden_size = int(hidden_size)
@@ -33,18 +36,18 @@ class GatedMLP(FeedForward):
     def tensors(self) -> dict[str, TensorSpec]:
         i, h = self.intermediate_size, self.hidden_size
         specs = {
-            "gate_proj.weight": TensorSpec((i, h)),
-            "up_proj.weight": TensorSpec((i, h)),
-            "down_proj.weight": TensorSpec((h, i)),
+            self.names["gate"]: TensorSpec((i, h)),
+            self.names["up"]: TensorSpec((i, h)),
+            self.names["down"]: TensorSpec((h, i)),
         }
         if self.bias:
             specs.update({"gate_proj.bias": TensorSpec((i,)), "up_proj.bias": TensorSpec((i,)), "down_proj.bias": TensorSpec((h,))})
         return specs
 
     def bind(self, tensors, dtype, device) -> None:
-        fused = torch.cat([tensors["gate_proj.weight"].to(dtype), tensors["up_proj.weight"].to(dtype)], dim=0)
+        fused = torch.cat([tensors[self.names["gate"]].to(dtype), tensors[self.names["up"]].to(dtype)], dim=0)
         self.w_gate_up = fused.to(device).contiguous()
-        self.w_down = tensors["down_proj.weight"].to(device=device, dtype=dtype).contiguous()
+        self.w_down = tensors[self.names["down"]].to(device=device, dtype=dtype).contiguous()
         if self.bias:
             self.b_gate_up = torch.cat([tensors["gate_proj.bias"].to(dtype), tensors["up_proj.bias"].to(dtype)]).to(device).contiguous()
             self.b_down = tensors["down_proj.bias"].to(device=device, dtype=dtype).contiguous()
@@ -101,3 +104,82 @@ class DenseMLP(FeedForward):
 
 
 register_part("feed_forward", "dense_mlp", DenseMLP)
+
+
+class RoutedMLP(FeedForward):
+    """A mixture of small feed-forward layers ``down_e(act(up_e(x)))`` without biases, of which each token uses ``top``:
+
+        z = W_router x (32-bit), s = softmax(z) over all experts
+        chosen: the ``top`` experts with the largest s + correction (``correction``: a tensor of the checkpoint)
+        weights: router_scale * s of the chosen ones (divided by their sum only with ``renormalize``)
+        out = sum over the chosen e of weight_e * expert_e(x)  +  sigmoid(w_sg . x) * shared(x)
+
+    ``shared_size``: the inner size of an expert that every token uses (None: none); ``shared_gate``: whether it is
+    multiplied by a sigmoid of one number per token.  Tensors: ``router``, ``correction``, ``e<i>.up``, ``e<i>.down``,
+    ``shared.up``, ``shared.down``, ``shared.sg``.
+
+    All experts' up matrices are stacked (the shared expert's last), so are the down matrices side by side: a step is
+    two matrix products over every expert with, between them, one kernel that applies the activation and the token's
+    weight of each expert's block of columns (0 for an expert the token did not choose, the gate for the shared one).
+    The second product then sums over the experts by itself.  Every weight matrix is read once a step whatever the
+    tokens chose, which is what a decode step of several requests costs anyway; a prompt pays the products of the
+    experts its tokens did not choose."""
+
+    graph_safe = True
+    accepts_sink = True
+
+    def __init__(self, hidden_size: int, experts: int, top: int, expert_size: int, activation: str = "relu2",
+                 router_scale: float = 1.0, correction: bool = True, renormalize: bool = False, shared_size: int | None = None,
+                 shared_gate: bool = True):
+        if activation not in DenseMLP.activations:
+            raise ValueError(f"activation {activation!r} is not built; known: {DenseMLP.activations}")
+        if not 1 <= int(top) <= int(experts):
+            raise ValueError(f"a token uses {top} of {experts} experts")
+        self.hidden_size, self.experts, self.top, self.expert_size = int(hidden_size), int(experts), int(top), int(expert_size)
+        self.activation, self.router_scale = activation, float(router_scale)
+        self.has_correction, self.renormalize = bool(correction), bool(renormalize)
+        self.shared_size = int(shared_size) if shared_size else 0
+        self.shared_gate = bool(shared_gate) and self.shared_size > 0
+        self.w_router = self.correction = self.w_up = self.w_down = None
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        h, f = self.hidden_size, self.expert_size
+        specs = {"router": TensorSpec((self.experts, h))}
+        if self.has_correction:
+            specs["correction"] = TensorSpec((self.experts,))
+        for e in range(self.experts):
+            specs[f"e{e}.up"] = TensorSpec((f, h))
+            specs[f"e{e}.down"] = TensorSpec((h, f))
+        if self.shared_size:
+            specs["shared.up"] = TensorSpec((self.shared_size, h))
+            specs["shared.down"] = TensorSpec((h, self.shared_size))
+            if self.shared_gate:
+                specs["shared.sg"] = TensorSpec((1, h))
+        return specs
+
+    def bind(self, tensors, dtype, device) -> None:
+        ups = [tensors[f"e{e}.up"] for e in range(self.experts)] + ([tensors["shared.up"]] if self.shared_size else [])
+        downs = [tensors[f"e{e}.down"] for e in range(self.experts)] + ([tensors["shared.down"]] if self.shared_size else [])
+        self.w_up = torch.cat([t.to(dtype) for t in ups], dim=0).to(device).contiguous()  # [E ff + shared, hidden]
+        self.w_down = torch.cat([t.to(dtype) for t in downs], dim=1).to(device).contiguous()  # [hidden, E ff + shared]
+        # the router (and the shared expert's gate as its last row) is a 32-bit product of its own
+        rows = [tensors["router"].float()] + ([tensors["shared.sg"].float().reshape(1, -1)] if self.shared_gate else [])
+        self.w_router = torch.cat(rows, dim=0).to(device).contiguous()
+        if self.has_correction:
+            self.correction = tensors["correction"].to(device=device, dtype=torch.float32).contiguous()
+
+    def forward(self, x, ctx, sink=None):
+        xt = x.materialize() if isinstance(x, ops.NormedInput) else x
+        z = ops.linear(xt if xt.dtype == torch.float32 else xt.float(), self.w_router)
+        weights = ops.route_topk(z, self.correction, self.experts, self.top, self.router_scale, self.renormalize, self.shared_gate)
+        if self.shared_size and not self.shared_gate:
+            weights = torch.cat((weights, torch.ones_like(weights[:, :1])), dim=1)
+        act = ops.expert_act_scale(ops.linear(xt, self.w_up), weights, self.experts, self.expert_size, self.activation)
+        if sink is not None:
+            handed_on = sink.linear(act, self.w_down)
+            if handed_on is not None:
+                return handed_on
+        return ops.linear(act, self.w_down, out_dtype=torch.float32)
+
+
+register_part("feed_forward", "routed_mlp", RoutedMLP)

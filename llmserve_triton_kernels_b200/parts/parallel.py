@@ -1,0 +1,66 @@
+"""Mixers side by side: every branch reads the same input, and their outputs meet as
+
+    factor * sum_b  rmsnorm(branch_b(x)) * w_b            (factor = 1 / branches: the mean)
+
+each output RMS-normed over the model width by itself (``eps`` inside the root) with a weight of its own.  A branch is
+any registered mixer; what it keeps per request (pages, a state slot) is its own: the cache manager holds every
+branch's as a part of a ``CompositeSpec``.  The branches' products leave their results in 32-bit, the norms and the
+sum are 32-bit, and the result is a contribution to the residual stream.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import CompositeSpec, Mixer, PartSpec, TensorSpec, build_part, register_part
+
+
+class ParallelMixer(Mixer):
+    def __init__(self, hidden_size: int, branches: dict[str, PartSpec], norm_eps: float, factor: float | None = None,
+                 weight_name: str = "out"):
+        """``branches``: name -> the mixer's spec; the name, with a dot, is the prefix of the branch's tensors, and
+        ``<name>.<weight_name>`` the weight of its output norm."""
+        if not 1 <= len(branches) <= 4:
+            raise ValueError(f"one to four branches run side by side, got {len(branches)}")
+        self.hidden_size, self.norm_eps, self.weight_name = int(hidden_size), float(norm_eps), weight_name
+        self.factor = 1.0 / len(branches) if factor is None else float(factor)
+        self.branch_names = tuple(branches)
+        for name, spec in branches.items():
+            setattr(self, f"branch_{name}", build_part("mixer", spec))
+        self.out_weights: list[torch.Tensor] = []
+
+    @property
+    def branches(self) -> list[Mixer]:
+        return [getattr(self, f"branch_{name}") for name in self.branch_names]
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(b.graph_safe for b in self.branches)
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        specs = {}
+        for name, branch in zip(self.branch_names, self.branches):
+            for local, spec in branch.tensors().items():
+                specs[f"{name}.{local}"] = spec
+            specs[f"{name}.{self.weight_name}"] = TensorSpec((self.hidden_size,), init="ones_plus_normal")
+        return specs
+
+    def bind(self, tensors, dtype, device) -> None:
+        self.out_weights = []
+        for name, branch in zip(self.branch_names, self.branches):
+            branch.bind({local: tensors[f"{name}.{local}"] for local in branch.tensors()}, dtype, device)
+            self.out_weights.append(tensors[f"{name}.{self.weight_name}"].to(device=device, dtype=torch.float32).contiguous())
+
+    def cache_spec(self) -> CompositeSpec:
+        return CompositeSpec(tuple(b.cache_spec() for b in self.branches))
+
+    def forward(self, x, ctx, cache):
+        outs = []
+        for branch, view in zip(self.branches, cache.parts):
+            out = branch.forward(x, ctx, view)
+            outs.append(out if out.dtype == torch.float32 else out.float())
+        return ops.branch_norm_sum(outs, self.out_weights, self.norm_eps, self.factor)
+
+
+register_part("mixer", "parallel", ParallelMixer)

@@ -1,4 +1,5 @@
-"""Element-wise gated recurrences with one state vector per request.
+"""Recurrences with a fixed-size state per request: an element-wise gated one (minGRU) and one whose state is a
+decaying matrix per head (retention).
 
 minGRU: the update gate and the candidate read only the current token,
 
@@ -61,3 +62,69 @@ class MinGRU(Mixer):
 
 
 register_part("mixer", "mingru", MinGRU)
+
+
+class Retention(Mixer):
+    """Linear attention with one fixed decay per head, no softmax and no denominator:
+
+        q = W_q x, k = W_k x (heads x dim), v = W_v x (heads x value_dim), g = W_g x
+        q, k: lanes i and i + rot/2 of every head turned by position * base^(-2i / rot); k then times dim^(-1/2)
+        S_t = decay_h S_(t-1) + k_t v_t^T        o_t = S_t^T q_t
+        out = W_o (unit_rms_per_head(o_t) * silu(g))
+
+    S ``[heads, dim, value_dim]`` starts at zero, is 32-bit and lives in the request's slot of the cache manager's
+    state tensor.  The four projections are one stacked product whose result stays 32-bit, so that what enters the
+    recurrence (rotated queries and keys, values) is; the norm of each head's o has no weight."""
+
+    graph_safe = True
+    accepts_sink = True
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, value_dim: int, decay: list[float], norm_eps: float,
+                 rotary: dict | None = None, gate: str = "silu", tensor_names: dict[str, str] | None = None):
+        if len(decay) != num_heads:
+            raise ValueError(f"{len(decay)} decays for {num_heads} heads")
+        if not 1 <= int(head_dim) <= 256:
+            raise ValueError(f"head_dim {head_dim}: the recurrence's kernel takes keys of up to 256 lanes")
+        self.hidden_size, self.num_heads, self.head_dim, self.value_dim = int(hidden_size), int(num_heads), int(head_dim), int(value_dim)
+        self.decay_values, self.norm_eps, self.gate = [float(d) for d in decay], float(norm_eps), gate
+        self.rotary = dict(rotary) if rotary and rotary.get("dims") else None
+        if self.rotary and not 0 < self.rotary["dims"] <= self.head_dim:
+            raise ValueError(f"rotary dims {self.rotary['dims']} do not fit a head of {self.head_dim}")
+        self.names = {"q": "q", "k": "k", "v": "v", "gate": "g", "out": "o", **(tensor_names or {})}
+        self.w_in = self.w_out = self.decay = self.freq = None
+        self.dtype: torch.dtype | None = None
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        n, h, qk, vv = self.names, self.hidden_size, self.num_heads * self.head_dim, self.num_heads * self.value_dim
+        return {n["q"]: TensorSpec((qk, h)), n["k"]: TensorSpec((qk, h)), n["v"]: TensorSpec((vv, h)),
+                n["gate"]: TensorSpec((vv, h)), n["out"]: TensorSpec((h, vv))}
+
+    def bind(self, tensors, dtype, device) -> None:
+        from .sigmoid_attention import rotary_frequencies
+
+        n = self.names
+        self.w_in = torch.cat([tensors[n[k]].to(dtype) for k in ("q", "k", "v", "gate")], dim=0).to(device).contiguous()
+        self.w_out = tensors[n["out"]].to(device=device, dtype=dtype).contiguous()
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float64).to(torch.float32).to(device)
+        if self.rotary:
+            self.freq = rotary_frequencies(self.rotary["dims"], self.rotary["base"], self.rotary.get("scaling")).to(device)
+        self.dtype = dtype
+
+    def cache_spec(self) -> StateSpec:
+        return StateSpec((self.num_heads, self.head_dim, self.value_dim), torch.float32)
+
+    def forward(self, x, ctx, cache, sink=None):
+        H, D, V = self.num_heads, self.head_dim, self.value_dim
+        proj = ops.linear(x, self.w_in, out_dtype=torch.float32)  # [N, q | k | v | gate], 32-bit
+        q, k = ops.qk_prepare(proj, ctx.positions, heads=H, kv_heads=H, dim=D, freq=self.freq, k_scale=D ** -0.5, out_dtype=torch.float32)
+        o = ops.retention_scan(q, k, proj[:, 2 * H * D : 2 * H * D + H * V], self.decay, cache.states, cache.slots, ctx.cu_tokens,
+                               ctx.num_requests, H, D, V)
+        out = ops.head_norm_gate(o, proj[:, 2 * H * D + H * V :], self.norm_eps, self.gate, out_dtype=self.dtype)
+        if sink is not None:
+            handed_on = sink.linear(out, self.w_out)
+            if handed_on is not None:
+                return handed_on
+        return ops.linear(out, self.w_out, out_dtype=torch.float32)
+
+
+register_part("mixer", "retention", Retention)

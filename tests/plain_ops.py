@@ -292,7 +292,132 @@ def biased_paged_attention(qkv, pool, page_table, ctx, *, num_heads, num_kv_head
     return out
 
 
+def qk_prepare(proj, positions, *, heads, kv_heads, dim, value_dim=0, freq=None, q_weight=None, k_weight=None, eps=0.0, k_scale=1.0,
+               pool=None, slot_map=None, out_dtype=None):
+    n = proj.shape[0]
+    q = proj[:, : heads * dim].float()
+    k = proj[:, heads * dim : (heads + kv_heads) * dim].float()
+    if q_weight is not None:
+        q = q / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight
+        k = k / torch.sqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight
+
+    def turn(x, count):
+        x = x.view(n, count, dim)
+        if freq is None or freq.numel() == 0:
+            return x
+        half = freq.numel()
+        angle = positions.float()[:, None] * freq[None, :]
+        c, s = angle.cos()[:, None, :], angle.sin()[:, None, :]
+        u, v = x[..., :half], x[..., half : 2 * half]
+        return torch.cat((u * c - v * s, v * c + u * s, x[..., 2 * half :]), dim=-1)
+
+    q, k = turn(q, heads).reshape(n, -1), turn(k, kv_heads) * k_scale
+    if pool is None:
+        out_dtype = out_dtype or proj.dtype
+        return q.to(out_dtype), k.reshape(n, -1).to(out_dtype)
+    v = proj[:, (heads + kv_heads) * dim : (heads + kv_heads) * dim + kv_heads * value_dim].view(n, kv_heads, value_dim)
+    page_size = pool.shape[3]
+    page, off = (slot_map // page_size).long(), (slot_map % page_size).long()
+    pool[page, 0, :, off, :dim] = k.to(pool.dtype)
+    pool[page, 1, :, off, :value_dim] = v.to(pool.dtype)
+    return q.to(pool.dtype)
+
+
+def sigmoid_attention(q, pool, page_table, ctx, *, num_heads, num_kv_heads, key_dim, value_dim, scale, softcap=None, head_bias=None,
+                      head_mix=None, window=None):
+    H, KV = num_heads, num_kv_heads
+    page_size = pool.shape[3]
+    out = torch.empty((q.shape[0], H * value_dim), dtype=q.dtype, device=q.device)
+    cu, lens = ctx.cu_tokens.tolist(), ctx.context_lens.tolist()
+    for r in range(len(lens)):
+        t0, t1, n = cu[r], cu[r + 1], lens[r]
+        pages = page_table[r, : -(-n // page_size)].long()
+        k = pool[pages, 0].float().permute(0, 2, 1, 3).reshape(-1, KV, pool.shape[4])[:n, :, :key_dim]
+        v = pool[pages, 1].float().permute(0, 2, 1, 3).reshape(-1, KV, pool.shape[4])[:n, :, :value_dim]
+        k, v = k.repeat_interleave(H // KV, dim=1), v.repeat_interleave(H // KV, dim=1)
+        qq = q[t0:t1].float().view(t1 - t0, H, key_dim)
+        s = torch.einsum("thd,jhd->htj", qq, k) * scale
+        if softcap:
+            s = softcap * torch.tanh(s / softcap)
+        if head_bias is not None:
+            s = s + head_bias.float()[:, None, None]
+        pos = torch.arange(n - (t1 - t0), n, device=q.device)[:, None]
+        j = torch.arange(n, device=q.device)[None, :]
+        visible = j <= pos
+        if window:
+            visible = visible & (j > pos - window)
+        p = torch.sigmoid(s) * visible[None]
+        if head_mix is not None:
+            p = torch.einsum("hg,gtj->htj", head_mix.float().view(H, H), p)
+        out[t0:t1] = torch.einsum("htj,jhd->thd", p, v).reshape(t1 - t0, -1).to(out.dtype)
+    return out
+
+
+def retention_scan(q, k, v, decay, states, state_slots, cu_tokens, num_requests, heads, dim, value_dim):
+    n = q.shape[0]
+    out = torch.empty((n, heads, value_dim), dtype=torch.float32, device=q.device)
+    cu, slots = cu_tokens.tolist(), state_slots.tolist()
+    g = decay.float()[:, None, None]
+    for r in range(num_requests):
+        S = states[slots[r]].clone()
+        for t in range(cu[r], cu[r + 1]):
+            kt, vt = k[t].float().view(heads, dim), v[t].float().view(heads, value_dim)
+            S = g * S + kt[:, :, None] * vt[:, None, :]
+            out[t] = torch.einsum("hdv,hd->hv", S, q[t].float().view(heads, dim))
+        states[slots[r]] = S
+    return out
+
+
+def head_norm_gate(o, gate, eps, kind="silu", out_dtype=torch.float32):
+    y = o.float()
+    if eps is not None:
+        y = y / torch.sqrt(y.pow(2).mean(-1, keepdim=True) + eps)
+    y = y.reshape(o.shape[0], -1)
+    if gate is not None:
+        z = gate.float()
+        y = y * (torch.sigmoid(z) if kind == "sigmoid" else z * torch.sigmoid(z))
+    return y.to(out_dtype)
+
+
+def route_topk(z, correction, experts, top, scale=1.0, renormalize=False, shared_gate=False):
+    s = torch.softmax(z[:, :experts].float(), dim=-1)
+    choice = s if correction is None else s + correction.float()
+    chosen = torch.zeros_like(s, dtype=torch.bool)
+    work = choice.clone()
+    for _ in range(top):  # the lowest index among equals, as the kernel
+        arg = work.argmax(dim=-1, keepdim=True)
+        chosen.scatter_(1, arg, True)
+        work.scatter_(1, arg, float("-inf"))
+    w = s * chosen * scale
+    if renormalize:
+        w = w / (s * chosen).sum(-1, keepdim=True)
+    if shared_gate:
+        w = torch.cat((w, torch.sigmoid(z[:, experts : experts + 1].float())), dim=1)
+    return w
+
+
+def expert_act_scale(x, weights, experts, ff, activation):
+    y = unary(x.float(), activation)
+    cols = torch.arange(x.shape[1], device=x.device)
+    block = torch.where(cols < experts * ff, cols // ff, torch.full_like(cols, experts))
+    return (y * weights[:, block]).to(x.dtype)
+
+
+def branch_norm_sum(branches, weights, eps, factor):
+    total = 0
+    for x, w in zip(branches, weights):
+        total = total + x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w
+    return total * factor
+
+
 ALL = (
+    "qk_prepare",
+    "sigmoid_attention",
+    "retention_scan",
+    "head_norm_gate",
+    "route_topk",
+    "expert_act_scale",
+    "branch_norm_sum",
     "group_rmsnorm",
     "stream_inject",
     "unary",
