@@ -230,6 +230,7 @@ LLM_EXPORT int llm_sigmoid_attention(const void* q, int q_dtype, int ldq, const 
     if (H <= 0 || KV <= 0 || H % KV || D <= 0 || V <= 0 || V > 256 || Dp < D || Dp < V || splits < 1 || split_keys < CHUNK ||
         split_keys % CHUNK || splits > 65535 || (splits > 1 && !parts) || q_dtype != pool_dtype || out_dtype != q_dtype)
         return LLM_ERR_BAD_ARGUMENT;
+    if (splits == 1) split_keys = 1 << 30;  // one CTA sums up all of a token's keys
     const int warps = H < 32 ? H : 32;
     const size_t smem = ((size_t)H * D + (size_t)H * CHUNK + (mix ? (size_t)32 * H : 0)) * sizeof(float);
     if (smem > 200 * 1024) return LLM_ERR_UNSUPPORTED;
