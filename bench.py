@@ -14,8 +14,9 @@ cache of the live requests) to its time; ``points`` holds decode at batch 1 and 
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from an earlier
 measurement on the same pool (and the line says which).
 
-``python bench.py --design nurolorn-small|nurolorn-1b`` prints, instead of the line, prefill and decode throughput of that
-Nurolorn configuration beside a Llama of equal width, depth and feed-forward size, and the design's kernels against their rooflines.
+``python bench.py --design nurolorn-small|nurolorn-1b|kafepel-small|kafepel-1b`` prints, instead of the line, prefill and decode
+throughput of that configuration beside a Llama of equal width, depth and feed-forward size, and the design's kernels against
+their rooflines.
 
 ``python bench.py --sweep [--steps K]`` prints no JSON line but two tables: decode steps over batch sizes and
 context lengths, and prefills over prompt lengths, timed the same way.
@@ -194,7 +195,7 @@ def prefill_flops(cfg, tokens: int) -> float:
 
 
 def design_comparison(args) -> int:
-    """Prefill and decode of a Nurolorn preset beside a Llama twin (the same width, as many layers as the design runs
+    """Prefill and decode of a preset of another design beside a Llama twin (the same width, as many layers as the design runs
     entries of its order, a SwiGLU feed-forward of the same parameter count, vocabulary and head size alike), both with
     random weights, through the same step function; then the design's kernels one by one against their rooflines.
     Every timed launch follows a write of 256 MB (larger than L2); times are CUDA events on the launching stream."""
@@ -216,10 +217,12 @@ def design_comparison(args) -> int:
     arch = architecture_of(design)
     dcfg = arch.config_class.from_dict(design)
     entries = len(arch.plan(dcfg).schedule)
-    width, ff, vocab = design["width"], design["layers"][0]["mlp"]["ff"], design["vocab"]
+    width, vocab = design["width"], design["vocab"]
+    ff = next(x["mlp"]["ff"] for x in design["layers"] if x.get("mlp") and "ff" in x["mlp"])
+    gated = design["architecture"] == "Kafepel"  # its dense feed-forward has three matrices, like the twin's
     twin = {
         "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_act": "silu", "rope_theta": 10000.0, "rms_norm_eps": 1e-5,
-        "tie_word_embeddings": False, "vocab_size": vocab, "hidden_size": width, "intermediate_size": (ff * 2 // 3 + 63) // 64 * 64,
+        "tie_word_embeddings": False, "vocab_size": vocab, "hidden_size": width, "intermediate_size": ff if gated else (ff * 2 // 3 + 63) // 64 * 64,
         "num_hidden_layers": entries, "num_attention_heads": width // 64, "num_key_value_heads": max(1, width // 512),
         "max_position_embeddings": 8192,
     }
@@ -306,12 +309,6 @@ def design_comparison(args) -> int:
                               max_context_len=max(context_lens), host_cu_tokens=cu)
         return ctx, table.to(device), i32(slots), page
 
-    L = next(x["mixer"] for x in design["layers"] if x["type"] == "latent_attention")
-    W = next(x["mixer"] for x in design["layers"] if x["type"] == "attention")
-    H, rank, rot, hd = L["heads"], L["kv_rank"], L["rot_dim"], L["dim"]
-    bf = torch.bfloat16
-    kernels = {}
-
     def hbm(name, us, nbytes, like=None):
         kernels[name] = {"us": round(us, 2), "GB_s": round(nbytes / us / 1e3), "of_hbm_peak": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 3)}
         if like:
@@ -322,6 +319,17 @@ def design_comparison(args) -> int:
         if like:
             kernels[name]["like"] = like
 
+    bf = torch.bfloat16
+    kernels = {}
+    if design["architecture"] == "Kafepel":
+        _kafepel_kernels(design, twin, ops, torch, timed, ctx_for, i32, hbm, tensor, device)
+        out["kernels"] = kernels
+        out["peaks"] = {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"]}
+        print(json.dumps(out, indent=1))
+        return 0
+    L = next(x["mixer"] for x in design["layers"] if x["type"] == "latent_attention")
+    W = next(x["mixer"] for x in design["layers"] if x["type"] == "attention")
+    H, rank, rot, hd = L["heads"], L["kv_rank"], L["rot_dim"], L["dim"]
     for label, qs, cs in (("prefill_2048", [2048], [2048]), ("decode_8x2048", [1] * 8, [2048] * 8)):
         ctx, table, slots, pages = ctx_for(qs, cs)
         n = ctx.num_tokens
@@ -383,6 +391,79 @@ def design_comparison(args) -> int:
     return 0
 
 
+def _kafepel_kernels(design, twin, ops, torch, timed, ctx_for, i32, hbm, tensor, device) -> None:
+    """The Kafepel design's own kernels, alone, at the preset's sizes: one request of 2,048 prompt tokens, and 8 decoding
+    requests of 2,048 cached tokens; the Llama twin's like kernel beside each."""
+    bf = torch.bfloat16
+    first = design["layers"][0]["mixer"]
+    A, R = first["left"], first["right"]
+    moe = next(x["mlp"] for x in design["layers"] if x["mlp"] and x["mlp"]["kind"] == "moe")
+    width = design["width"]
+    H, KV, D, V = A["heads"], A["kv_heads"], A["dim"], A["vdim"]
+    for label, qs, cs in (("prefill_2048", [2048], [2048]), ("decode_8x2048", [1] * 8, [2048] * 8)):
+        ctx, table, slots, pages = ctx_for(qs, cs)
+        n = ctx.num_tokens
+        pairs = sum(q * c - q * (q - 1) // 2 for q, c in zip(qs, cs))
+        prefill = label.startswith("prefill")
+        pool = torch.randn(pages, 2, KV, 16, max(D, V), device=device).to(bf)
+        q = (torch.randn(n, H * D, device=device) * 0.3).to(bf)
+        bias, mix = torch.zeros(H, device=device), torch.randn(H, H, device=device)
+        kw = dict(num_heads=H, num_kv_heads=KV, key_dim=D, value_dim=V, scale=A["scale"], softcap=A.get("softcap"), head_bias=bias, head_mix=mix)
+        us = timed(lambda: ops.sigmoid_attention(q, pool, table, ctx, **kw))
+        if prefill:  # the products with keys and values; the mixing of the heads' weights (2 H flops a weight, 32-bit) is not counted
+            tensor(f"sigmoid_attention_{label}", us, 2.0 * H * (D + V) * pairs, like="Llama prefill attention (tcgen05)")
+        else:
+            hbm(f"sigmoid_attention_{label}", us, sum(cs) * KV * (D + V) * 2, like="Llama decode attention (split keys)")
+        tH, tKV = twin["num_attention_heads"], twin["num_key_value_heads"]
+        tpool = torch.randn(pages, 2, tKV, 16, 64, device=device).to(bf)
+        tq = torch.randn(n, (tH + 2 * tKV) * 64, device=device).to(bf)
+        us = timed(lambda: ops.paged_attention(tq, tpool, table, ctx, num_heads=tH, num_kv_heads=tKV, head_dim=64, scale=0.125))
+        if prefill:
+            tensor(f"llama_attention_{label}", us, 4.0 * tH * 64 * pairs)
+        else:
+            hbm(f"llama_attention_{label}", us, sum(cs) * 2 * tKV * 64 * 2)
+        # projections -> queries, keys in their pages
+        proj = torch.randn(n, (H + KV) * D + KV * V, device=device)
+        freq = torch.rand(D // 2, device=device)
+        qw, kwt = torch.ones(H * D, device=device), torch.ones(KV * D, device=device)
+        us = timed(lambda: ops.qk_prepare(proj, ctx.positions, heads=H, kv_heads=KV, dim=D, value_dim=V, freq=freq, q_weight=qw, k_weight=kwt,
+                                          eps=1e-6, pool=pool, slot_map=slots))
+        hbm(f"qk_prepare_{label}", us, n * ((H + KV) * D + KV * V) * (4 + 2), like="llama_rope_kv_write")
+        table_r = torch.randn(4096, 64, device=device)
+        us = timed(lambda: ops.rope_kv_write(tq, ctx.positions, table_r, slots, tpool, tH, tKV, 64))
+        hbm(f"llama_rope_kv_write_{label}", us, n * ((tH + tKV) * 64 * 4 + tKV * 64 * 4))
+        # retention: the scan and the step behind it
+        RH, RD, RV = R["heads"], R["dim"], R["vdim"]
+        rq, rk = torch.randn(n, RH * RD, device=device), torch.randn(n, RH * RD, device=device) * RD ** -0.5
+        rv = torch.randn(n, RH * RV, device=device)
+        decay = torch.tensor(R["decay"], dtype=torch.float32, device=device)
+        states, sl = torch.zeros(8, RH, RD, RV, device=device), i32(list(range(len(qs))))
+        us = timed(lambda: ops.retention_scan(rq, rk, rv, decay, states, sl, ctx.cu_tokens, len(qs), RH, RD, RV))
+        hbm(f"retention_scan_{label}", us, n * RH * (2 * RD + 2 * RV) * 4 + 2 * len(qs) * RH * RD * RV * 4, like="(no like kernel in Llama)")
+        o, gate = torch.randn(n, RH, RV, device=device), torch.randn(n, RH * RV, device=device)
+        us = timed(lambda: ops.head_norm_gate(o, gate, 1e-6, "silu", bf))
+        hbm(f"head_norm_gate_{label}", us, n * RH * RV * (4 + 4 + 2), like="llama_swiglu")
+        a, b, wn = torch.randn(n, width, device=device), torch.randn(n, width, device=device), torch.ones(width, device=device)
+        us = timed(lambda: ops.branch_norm_sum([a, b], [wn, wn], 1e-6, 0.5))
+        hbm(f"branch_norm_sum_{label}", us, n * width * 12, like="llama_rmsnorm")
+        resid = torch.randn(n, width, device=device)
+        us = timed(lambda: ops.rmsnorm(resid, wn, 1e-6, delta=a, out_dtype=bf))
+        hbm(f"llama_rmsnorm_{label}", us, n * width * (4 + 4 + 4 + 2))
+        # routed feed-forward: the choice, and the activation with the tokens' weights
+        E, top, eff, sff = moe["router"]["experts"], moe["router"]["top"], moe["expert"]["ff"], moe["shared"]["ff"]
+        z = torch.randn(n, E + 1, device=device)
+        corr = torch.zeros(E, device=device)
+        us = timed(lambda: ops.route_topk(z, corr, E, top, 2.5, False, True))
+        hbm(f"route_topk_{label}", us, n * (2 * E + 2) * 4, like="(no like kernel in Llama)")
+        weights = ops.route_topk(z, corr, E, top, 2.5, False, True)
+        up = torch.randn(n, E * eff + sff, device=device).to(bf)
+        us = timed(lambda: ops.expert_act_scale(up, weights, E, eff, "relu2"))
+        hbm(f"expert_act_scale_{label}", us, n * (E * eff + sff) * 4, like="llama_swiglu")
+        gu = torch.randn(n, 2 * twin["intermediate_size"], device=device).to(bf)
+        us = timed(lambda: ops.swiglu(gu))
+        hbm(f"llama_swiglu_{label}", us, n * twin["intermediate_size"] * 6)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -395,8 +476,8 @@ def main() -> int:
                          "fixed number of pages, with preemption")
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (recorded in config)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64, the end-to-end run and the kernel table")
-    ap.add_argument("--design", choices=["nurolorn-small", "nurolorn-1b"], default=None,
-                    help="instead of the one line: prefill and decode throughput of a Nurolorn configuration beside a Llama of "
+    ap.add_argument("--design", choices=["nurolorn-small", "nurolorn-1b", "kafepel-small", "kafepel-1b"], default=None,
+                    help="instead of the one line: prefill and decode throughput of a Nurolorn or Kafepel configuration beside a Llama of "
                          "equal width, depth and feed-forward size, and the design's own kernels against their rooflines")
     ap.add_argument("--sweep", action="store_true",
                     help="instead of the one line: a table of decode steps over batch sizes and context lengths and of prefills over prompt lengths")

@@ -38,7 +38,28 @@ def _nurolorn(width: int, ff: int, heads: int, rank: int, rot: int, window: int,
     }
 
 
+def _kafepel(width: int, layers: int, heads: int, kv_heads: int, ff: int, experts: int, top: int, expert_ff: int, shared_ff: int,
+             vocab: int = 32000) -> dict:
+    """Layers alternate between a dense and a routed feed-forward; the attention branch has heads of 64 lanes, the
+    retention branch half as many heads with keys of 64 and values of 128 lanes (decays ``1 - 2^-(5 + h/2)``)."""
+    head = 64
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5, "softcap": 30.0,
+            "rot": {"base": 500000.0, "dims": head, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    r_heads = heads // 2
+    right = {"heads": r_heads, "dim": head, "vdim": 2 * head, "decay": [1.0 - 2.0 ** -(5.0 + h / 2.0) for h in range(r_heads)],
+             "rot": {"base": 10000.0, "dims": head}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 2.5}, "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff}}
+    return {
+        "architecture": "Kafepel", "vocab": vocab, "width": width, "embedding": {"scale": float(width) ** 0.5}, "norm": {"eps": 1e-6},
+        "layers": [{"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": dense if i % 2 == 0 else moe} for i in range(layers)],
+    }
+
+
 PRESETS: dict[str, dict] = {
+    # Kafepel at sizes that resemble real layers (the design has no published sizes)
+    "kafepel-small": _kafepel(1024, 8, 16, 4, 2816, 16, 2, 512, 1024),
+    "kafepel-1b": _kafepel(2048, 12, 32, 8, 5632, 32, 4, 704, 1408),
     # Nurolorn at sizes that resemble real layers (the design has no published sizes): a stretch of four layers runs twice
     "nurolorn-small": _nurolorn(1024, 4096, 16, 128, 32, 512, "LLGWLL", (1, 5, 2)),
     "nurolorn-1b": _nurolorn(2048, 8192, 32, 256, 32, 1024, "LLGWLLGWLL", (2, 8, 2)),

@@ -14,21 +14,67 @@ namespace {
 constexpr int COLS = 16;  // columns of the state a CTA owns
 constexpr int TPC = 8;    // threads a column
 
+__device__ __forceinline__ void attn_cp16(float* smem, const float* gmem) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(gmem));
+}
+
 // q, k: [N, H, D] float32 (row pitches ldq, ldk); v: [N, H, V] (pitch ldv, any type); states: [slots, H, D, V]
 // out: [N, H, V] float32
-template <typename TV, int DPT>
+// The tokens come through shared memory in blocks of TB (queries and keys of the head, the CTA's 16 lanes of the
+// values), the next block on its way (cp.async) while one is walked; thread (column, part) holds rows
+// part * DPT .. part * DPT + DPT - 1 of its column.  Only S is carried from token to token: the sums o_t of
+// neighbouring tokens overlap.
+template <typename TV, int DPT, int TB>
 __global__ void __launch_bounds__(COLS * TPC)
 retention_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk, const TV* __restrict__ v, int ldv,
                       const float* __restrict__ decay, float* __restrict__ states, const int* __restrict__ state_slots,
                       const int* __restrict__ cu_tokens, float* __restrict__ out, int H, int D, int V) {
-    extern __shared__ float tile[];  // [D][COLS + 1]
+    constexpr int DS = DPT * TPC;  // rows of the state that the CTA's registers have room for (>= D)
+    extern __shared__ __align__(16) float shared[];
+    float* tile = shared;                       // [DS][COLS + 1], the state on its way in and out
+    float* sq = tile + DS * (COLS + 1);         // [2][TB][DS]
+    float* sk = sq + 2 * TB * DS;               // [2][TB][DS]
+    float* sv = sk + 2 * TB * DS;               // [2][TB][COLS]
     pdl_trigger();
     const int r = blockIdx.z, h = blockIdx.y, v0 = blockIdx.x * COLS;
     const int sub = threadIdx.x % TPC, col = threadIdx.x / TPC;
     const int begin = cu_tokens[r], end = cu_tokens[r + 1], slot = state_slots[r];
     const float gamma = decay[h];
     float* state = states + ((size_t)slot * H + h) * D * V;
+    const bool vec = (D % 4 == 0) && (ldq % 4 == 0) && (ldk % 4 == 0) && ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k)) % 16 == 0);  // rows of q and k may be copied 16 bytes at a time
     pdl_wait();
+
+    auto fetch = [&](int t0, int buf) {
+        const int count = min(TB, end - t0);
+        if (vec) {
+            const int chunks = D / 4;
+            for (int i = threadIdx.x; i < count * chunks; i += blockDim.x) {
+                const int tt = i / chunks, ch = i % chunks;
+                attn_cp16(sq + ((size_t)buf * TB + tt) * DS + ch * 4, q + (size_t)(t0 + tt) * ldq + (size_t)h * D + ch * 4);
+                attn_cp16(sk + ((size_t)buf * TB + tt) * DS + ch * 4, k + (size_t)(t0 + tt) * ldk + (size_t)h * D + ch * 4);
+            }
+        } else {
+            for (int i = threadIdx.x; i < count * D; i += blockDim.x) {
+                const int tt = i / D, d = i % D;
+                sq[((size_t)buf * TB + tt) * DS + d] = q[(size_t)(t0 + tt) * ldq + (size_t)h * D + d];
+                sk[((size_t)buf * TB + tt) * DS + d] = k[(size_t)(t0 + tt) * ldk + (size_t)h * D + d];
+            }
+        }
+        for (int i = threadIdx.x; i < count * COLS; i += blockDim.x) {
+            const int tt = i / COLS, c = i % COLS;
+            sv[((size_t)buf * TB + tt) * COLS + c] = v0 + c < V ? to_float(v[(size_t)(t0 + tt) * ldv + (size_t)h * V + v0 + c]) : 0.f;
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+
+    if (begin < end) fetch(begin, 0);
+    // lanes of q and k beyond D (the registers' room is a multiple of 8 * DPT) are zeros in both buffers
+    for (int i = threadIdx.x; i < 2 * TB * (DS - D); i += blockDim.x) {
+        const int row = i / (DS - D), d = D + i % (DS - D);
+        sq[(size_t)row * DS + d] = 0.f;
+        sk[(size_t)row * DS + d] = 0.f;
+    }
     for (int i = threadIdx.x; i < D * COLS; i += blockDim.x) {
         const int d = i / COLS, c = i % COLS;
         tile[d * (COLS + 1) + c] = v0 + c < V ? state[(size_t)d * V + v0 + c] : 0.f;
@@ -37,37 +83,46 @@ retention_scan_kernel(const float* __restrict__ q, int ldq, const float* __restr
     float S[DPT];
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-        const int d = sub + TPC * i;
+        const int d = sub * DPT + i;
         S[i] = d < D ? tile[d * (COLS + 1) + col] : 0.f;
     }
     const bool live = v0 + col < V;
-    const int vc = live ? v0 + col : V - 1;
-    for (int t = begin; t < end; ++t) {
-        const float* qt = q + (size_t)t * ldq + (size_t)h * D;
-        const float* kt = k + (size_t)t * ldk + (size_t)h * D;
-        const float vt = to_float(v[(size_t)t * ldv + (size_t)h * V + vc]);
-        float kk[DPT], qq[DPT];
+    int buf = 0;
+    for (int t0 = begin; t0 < end; t0 += TB, buf ^= 1) {
+        asm volatile("cp.async.wait_group 0;\n" ::);
+        __syncthreads();  // this block has landed, and everybody has left the other buffer
+        if (t0 + TB < end) fetch(t0 + TB, buf ^ 1);
+        const int count = min(TB, end - t0);
+        const float* bq = sq + (size_t)buf * TB * DS + sub * DPT;
+        const float* bk = sk + (size_t)buf * TB * DS + sub * DPT;
+        const float* bv = sv + (size_t)buf * TB * COLS + col;
+#pragma unroll 4
+        for (int tt = 0; tt < count; ++tt) {
+            const float vt = bv[tt * COLS];
+            float o = 0.f;
 #pragma unroll
-        for (int i = 0; i < DPT; ++i) {
-            const int d = sub + TPC * i;
-            kk[i] = d < D ? kt[d] : 0.f;
-            qq[i] = d < D ? qt[d] : 0.f;
+            for (int i = 0; i < DPT; i += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(bk + (size_t)tt * DS + i);
+                const float4 q4 = *reinterpret_cast<const float4*>(bq + (size_t)tt * DS + i);
+                S[i] = fmaf(gamma, S[i], k4.x * vt);
+                S[i + 1] = fmaf(gamma, S[i + 1], k4.y * vt);
+                S[i + 2] = fmaf(gamma, S[i + 2], k4.z * vt);
+                S[i + 3] = fmaf(gamma, S[i + 3], k4.w * vt);
+                o = fmaf(S[i], q4.x, o);
+                o = fmaf(S[i + 1], q4.y, o);
+                o = fmaf(S[i + 2], q4.z, o);
+                o = fmaf(S[i + 3], q4.w, o);
+            }
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            o += __shfl_xor_sync(0xffffffffu, o, 4);
+            if (sub == 0 && live) out[((size_t)(t0 + tt) * H + h) * V + v0 + col] = o;
         }
-        float o = 0.f;
-#pragma unroll
-        for (int i = 0; i < DPT; ++i) {
-            S[i] = fmaf(gamma, S[i], kk[i] * vt);
-            o = fmaf(S[i], qq[i], o);
-        }
-        o += __shfl_xor_sync(0xffffffffu, o, 1);
-        o += __shfl_xor_sync(0xffffffffu, o, 2);
-        o += __shfl_xor_sync(0xffffffffu, o, 4);
-        if (sub == 0 && live) out[((size_t)t * H + h) * V + v0 + col] = o;
     }
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-        const int d = sub + TPC * i;
+        const int d = sub * DPT + i;
         if (d < D) tile[d * (COLS + 1) + col] = S[i];
     }
     __syncthreads();
@@ -112,16 +167,22 @@ LLM_EXPORT int llm_retention_scan(const float* q, int ldq, const float* k, int l
     if (requests <= 0) return 0;
     if (H <= 0 || D <= 0 || V <= 0 || D > 256 || requests > 65535 || H > 65535) return LLM_ERR_BAD_ARGUMENT;
     const dim3 grid((V + COLS - 1) / COLS, H, requests), block(COLS * TPC);
-    const size_t smem = (size_t)D * (COLS + 1) * sizeof(float);
     using bf = __nv_bfloat16;
-    auto go = [&](auto kernel, auto* vp) {
+    auto go = [&](auto kernel, auto* vp, int dpt, int tb) -> int {
+        const int ds = dpt * TPC;
+        const size_t smem = ((size_t)ds * (COLS + 1) + (size_t)4 * tb * ds + (size_t)2 * tb * COLS) * sizeof(float);
+        if (smem > 48 * 1024) {
+            const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
         return launch_pdl(kernel, grid, block, smem, stream, q, ldq, k, ldk, vp, ldv, decay, states, state_slots, cu_tokens, out, H, D, V);
     };
-#define LLM_RET(DPT) (v_dtype == LLM_F32 ? go(retention_scan_kernel<float, DPT>, (const float*)v) : go(retention_scan_kernel<bf, DPT>, (const bf*)v))
-    if (D <= 32) return LLM_RET(4);
-    if (D <= 64) return LLM_RET(8);
-    if (D <= 128) return LLM_RET(16);
-    return LLM_RET(32);
+#define LLM_RET(DPT, TB) \
+    (v_dtype == LLM_F32 ? go(retention_scan_kernel<float, DPT, TB>, (const float*)v, DPT, TB) : go(retention_scan_kernel<bf, DPT, TB>, (const bf*)v, DPT, TB))
+    if (D <= 32) return LLM_RET(4, 32);
+    if (D <= 64) return LLM_RET(8, 32);
+    if (D <= 128) return LLM_RET(16, 16);
+    return LLM_RET(32, 8);
 #undef LLM_RET
 }
 

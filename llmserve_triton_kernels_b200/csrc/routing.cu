@@ -79,7 +79,30 @@ __device__ __forceinline__ float activate(float v, int kind) {
 }
 
 // y[t, j] = act(x[t, j]) * w[t, block(j)]: block(j) = j / ff for j < E * ff, and E for the columns behind them (a
-// shared expert's).  x, y: [N, C].
+// shared expert's).  x, y: [N, C].  In two forms: 16 bytes a thread, where every run of 16 bytes lies within one expert's
+// block (ff a multiple of the run) and rows start on 16-byte boundaries; element by element elsewhere.
+template <typename T>
+__global__ void __launch_bounds__(256)
+expert_act_scale_wide_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w, int ldw, T* __restrict__ y, int ldy, int N, int C,
+                             int E, int ff, int kind) {
+    constexpr int RUN = 16 / sizeof(T);
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.y;
+    for (int j = (blockIdx.x * blockDim.x + threadIdx.x) * RUN; j < C; j += gridDim.x * blockDim.x * RUN) {
+        const int b = j < E * ff ? j / ff : E;
+        const float wt = w[(size_t)t * ldw + b];
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        T* v = reinterpret_cast<T*>(&raw);
+        if (wt != 0.f) {
+            raw = *reinterpret_cast<const uint4*>(x + (size_t)t * ldx + j);
+#pragma unroll
+            for (int e = 0; e < RUN; ++e) v[e] = from_float<T>(activate(to_float(v[e]), kind) * wt);
+        }
+        *reinterpret_cast<uint4*>(y + (size_t)t * ldy + j) = raw;
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 expert_act_scale_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w, int ldw, T* __restrict__ y, int ldy, int N, int C,
@@ -135,6 +158,15 @@ LLM_EXPORT int llm_expert_act_scale(const void* x, int ldx, const float* w, int 
                                     int ff, int kind, cudaStream_t stream) {
     if (N <= 0 || C <= 0) return 0;
     if (E < 0 || ff <= 0 || (size_t)E * ff > (size_t)C || N > 65535) return LLM_ERR_BAD_ARGUMENT;
+    const int run = dtype == LLM_F32 ? 4 : 8;
+    if (ff % run == 0 && C % run == 0 && ldx % run == 0 && ldy % run == 0 && ((uintptr_t)x | (uintptr_t)y) % 16 == 0) {
+        const int per = 256 * run, blocks = (C + per - 1) / per;
+        const dim3 grid(blocks < 64 ? blocks : 64, N), block(256);
+        if (dtype == LLM_F32)
+            return launch_pdl(expert_act_scale_wide_kernel<float>, grid, block, 0, stream, (const float*)x, ldx, w, ldw, (float*)y, ldy, N, C, E, ff, kind);
+        return launch_pdl(expert_act_scale_wide_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)x, ldx, w, ldw,
+                          (__nv_bfloat16*)y, ldy, N, C, E, ff, kind);
+    }
     const dim3 grid((C + 255) / 256 < 64 ? (C + 255) / 256 : 64, N), block(256);
     if (dtype == LLM_F32)
         return launch_pdl(expert_act_scale_kernel<float>, grid, block, 0, stream, (const float*)x, ldx, w, ldw, (float*)y, ldy, N, C, E, ff, kind);

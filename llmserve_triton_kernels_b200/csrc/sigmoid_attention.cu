@@ -45,6 +45,9 @@ sigmoid_attention_kernel(const TQ* __restrict__ q, int ldq, const TC* __restrict
     const int group = H / KV;
     pdl_trigger();
     const int pos = positions[t], req = token_request[t];
+    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    // a stretch none of whose keys the token sees leaves its partial sums unwritten: the sum reads only stretches that have some
+    if (splits > 1 && (split * split_keys > pos || (split + 1) * split_keys <= first)) return;
     const int* table = page_table + (size_t)req * table_width;
     if (mix)
         for (int i = threadIdx.x; i < 32 * H; i += blockDim.x) {
@@ -54,7 +57,6 @@ sigmoid_attention_kernel(const TQ* __restrict__ q, int ldq, const TC* __restrict
     pdl_wait();
     for (int i = threadIdx.x; i < H * D; i += blockDim.x) sq[i] = to_float(q[(size_t)t * ldq + i]);
     __syncthreads();
-    int first = window > 0 ? max(0, pos - window + 1) : 0;
     int j_lo = max(first, split * split_keys), j_hi = min(pos, (split + 1) * split_keys - 1);  // inclusive
     float acc[VPL];
 #pragma unroll
@@ -127,13 +129,16 @@ sigmoid_attention_kernel(const TQ* __restrict__ q, int ldq, const TC* __restrict
 // out[i] = sum over the stretches, in their order, of part[s][i]
 template <typename TO>
 __global__ void __launch_bounds__(256)
-sum_parts_kernel(const float* __restrict__ part, TO* __restrict__ out, size_t count, int splits) {
+sum_parts_kernel(const float* __restrict__ part, TO* __restrict__ out, const int* __restrict__ positions, int row, size_t count,
+                 int split_keys, int window) {
     pdl_trigger();
-    pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= count) return;
+    const int pos = positions[i / row];
+    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    pdl_wait();
     float s = 0.f;
-    for (int k = 0; k < splits; ++k) s += part[(size_t)k * count + i];
+    for (int k = first / split_keys; k <= pos / split_keys; ++k) s += part[(size_t)k * count + i];
     out[i] = from_float<TO>(s);
 }
 
@@ -258,8 +263,19 @@ LLM_EXPORT int llm_sigmoid_attention(const void* q, int q_dtype, int ldq, const 
     if (code != 0 || splits == 1) return code;
     const size_t count = (size_t)N * H * V;
     const dim3 g2((unsigned)((count + 255) / 256));
-    if (out_dtype == LLM_F32) return launch_pdl(sum_parts_kernel<float>, g2, dim3(256), 0, stream, (const float*)parts, (float*)out, count, splits);
-    return launch_pdl(sum_parts_kernel<bf>, g2, dim3(256), 0, stream, (const float*)parts, (bf*)out, count, splits);
+    if (out_dtype == LLM_F32)
+        return launch_pdl(sum_parts_kernel<float>, g2, dim3(256), 0, stream, (const float*)parts, (float*)out, positions, H * V, count, split_keys, window);
+    return launch_pdl(sum_parts_kernel<bf>, g2, dim3(256), 0, stream, (const float*)parts, (bf*)out, positions, H * V, count, split_keys, window);
+}
+
+// out[t, :] = the sum of parts[s][t, :] over the stretches s in which token t has keys, in their order.
+LLM_EXPORT int llm_sigmoid_sum_parts(const float* parts, void* out, int out_dtype, const int* positions, int N, int row, int split_keys,
+                                     int window, cudaStream_t stream) {
+    if (N <= 0 || row <= 0) return 0;
+    const size_t count = (size_t)N * row;
+    const dim3 grid((unsigned)((count + 255) / 256));
+    if (out_dtype == LLM_F32) return launch_pdl(sum_parts_kernel<float>, grid, dim3(256), 0, stream, parts, (float*)out, positions, row, count, split_keys, window);
+    return launch_pdl(sum_parts_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, parts, (__nv_bfloat16*)out, positions, row, count, split_keys, window);
 }
 
 // in_dtype: the projections' type; q_dtype: the queries' type on their way out; k_dtype: the keys' (and the pool's).

@@ -59,6 +59,8 @@ _SIGNATURES = {
     "llm_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "llm_sigmoid_attention": [_vp, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i,
                               _i, _i, _vp],
+    "llm_sigmoid_attention_mma": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i, _i, _vp],
+    "llm_sigmoid_sum_parts": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
     "llm_qk_prepare": [_vp, _i, _i, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _f, _vp, _i, _vp, _f, _i, _i, _i, _i, _i, _vp],
     "llm_retention_scan": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "llm_head_norm_gate": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _i, _vp],
@@ -1208,13 +1210,31 @@ def sigmoid_attention(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Ten
     longest = getattr(ctx, "max_context_len", None) or int(ctx.context_lens.max())
     if window:
         longest = min(longest, window + ctx.max_query_len)
-    splits = 1 if n > _SIGMOID_SPLIT_MAX_TOKENS else max(1, min(-(-longest // _SIGMOID_SPLIT_KEYS), 1024))
+    split_keys = max(_SIGMOID_SPLIT_KEYS, -(-longest // (1024 * 32)) * 32)  # at most 1,024 stretches, of whole chunks of 32 keys
+    splits = 1 if n > _SIGMOID_SPLIT_MAX_TOKENS else max(1, -(-longest // split_keys))
     parts = torch.empty((splits, n, num_heads * value_dim), dtype=torch.float32, device=q.device) if splits > 1 else None
+    if q.dtype == torch.bfloat16 and not _FORCE_GENERIC_ATTENTION:
+        # the tensor cores: tiles of 16 tokens of one request
+        cu = getattr(ctx, "host_cu_tokens", None) or ctx.cu_tokens.tolist()
+        tiles = sum(-(-(b - a) // 16) for a, b in zip(cu[:-1], cu[1:]))
+        code = _launch(
+            "llm_sigmoid_attention_mma", _ptr(q), q.stride(0), _ptr(pool), _ptr(page_table), page_table.shape[1], _ptr(ctx.positions),
+            _ptr(ctx.cu_tokens), _ptr(head_bias), _ptr(head_mix), _ptr(out), _ptr(parts), tiles, n, len(cu) - 1, num_heads, num_kv_heads,
+            key_dim, value_dim, pool.shape[4], pool.shape[3], float(scale), float(softcap or 0.0), int(window or 0), split_keys, splits,
+            _stream(),
+        )
+        if code != 10002:
+            _check(code, "sigmoid_attention (tensor cores)")
+            if splits > 1:
+                _check(_launch("llm_sigmoid_sum_parts", _ptr(parts), _ptr(out), _code(out.dtype), _ptr(ctx.positions), n,
+                               num_heads * value_dim, split_keys, int(window or 0), _stream()), "sigmoid_attention (sum of the stretches)")
+            return out
+        add_launches(-1)  # sizes the kernel does not take: the general one below
     code = _launch(
         "llm_sigmoid_attention", _ptr(q), _code(q.dtype), q.stride(0), _ptr(pool), _code(pool.dtype), _ptr(page_table),
         page_table.shape[1], _ptr(ctx.positions), _ptr(ctx.token_request), _ptr(head_bias), _ptr(head_mix), _ptr(out),
         _code(out.dtype), _ptr(parts), n, num_heads, num_kv_heads, key_dim, value_dim, pool.shape[4], pool.shape[3], float(scale),
-        float(softcap or 0.0), int(window or 0), _SIGMOID_SPLIT_KEYS, splits, _stream(),
+        float(softcap or 0.0), int(window or 0), split_keys, splits, _stream(),
     )
     _check(code, "sigmoid_attention")
     add_launches(int(splits > 1))
