@@ -30,12 +30,14 @@ __global__ void __launch_bounds__(COLS * TPC)
 retention_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk, const TV* __restrict__ v, int ldv,
                       const float* __restrict__ decay, float* __restrict__ states, const int* __restrict__ state_slots,
                       const int* __restrict__ cu_tokens, float* __restrict__ out, int H, int D, int V) {
-    constexpr int DS = DPT * TPC;  // rows of the state that the CTA's registers have room for (>= D)
+    constexpr int DS = DPT * TPC;   // rows of the state that the CTA's registers have room for (>= D)
+    constexpr int SEG = DPT + 4;    // a part's lanes of a token's q or k, then 4 floats of room: the parts' 16-byte reads fall
+    constexpr int RP = SEG * TPC;   // into different banks; RP: the pitch of a token's row
     extern __shared__ __align__(16) float shared[];
     float* tile = shared;                       // [DS][COLS + 1], the state on its way in and out
-    float* sq = tile + DS * (COLS + 1);         // [2][TB][DS]
-    float* sk = sq + 2 * TB * DS;               // [2][TB][DS]
-    float* sv = sk + 2 * TB * DS;               // [2][TB][COLS]
+    float* sq = tile + DS * (COLS + 1);         // [2][TB][RP]
+    float* sk = sq + 2 * TB * RP;               // [2][TB][RP]
+    float* sv = sk + 2 * TB * RP;               // [2][TB][COLS]
     pdl_trigger();
     const int r = blockIdx.z, h = blockIdx.y, v0 = blockIdx.x * COLS;
     const int sub = threadIdx.x % TPC, col = threadIdx.x / TPC;
@@ -45,25 +47,35 @@ retention_scan_kernel(const float* __restrict__ q, int ldq, const float* __restr
     const bool vec = (D % 4 == 0) && (ldq % 4 == 0) && (ldk % 4 == 0) && ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k)) % 16 == 0);  // rows of q and k may be copied 16 bytes at a time
     pdl_wait();
 
+    const bool vec_v = sizeof(TV) == 4 && V % 4 == 0 && ldv % 4 == 0 && reinterpret_cast<uintptr_t>(v) % 16 == 0 && v0 + COLS <= V;
     auto fetch = [&](int t0, int buf) {
         const int count = min(TB, end - t0);
         if (vec) {
             const int chunks = D / 4;
             for (int i = threadIdx.x; i < count * chunks; i += blockDim.x) {
-                const int tt = i / chunks, ch = i % chunks;
-                attn_cp16(sq + ((size_t)buf * TB + tt) * DS + ch * 4, q + (size_t)(t0 + tt) * ldq + (size_t)h * D + ch * 4);
-                attn_cp16(sk + ((size_t)buf * TB + tt) * DS + ch * 4, k + (size_t)(t0 + tt) * ldk + (size_t)h * D + ch * 4);
+                const int tt = i / chunks, d = (i % chunks) * 4;
+                const int at = (d / DPT) * SEG + d % DPT;
+                attn_cp16(sq + ((size_t)buf * TB + tt) * RP + at, q + (size_t)(t0 + tt) * ldq + (size_t)h * D + d);
+                attn_cp16(sk + ((size_t)buf * TB + tt) * RP + at, k + (size_t)(t0 + tt) * ldk + (size_t)h * D + d);
             }
         } else {
             for (int i = threadIdx.x; i < count * D; i += blockDim.x) {
                 const int tt = i / D, d = i % D;
-                sq[((size_t)buf * TB + tt) * DS + d] = q[(size_t)(t0 + tt) * ldq + (size_t)h * D + d];
-                sk[((size_t)buf * TB + tt) * DS + d] = k[(size_t)(t0 + tt) * ldk + (size_t)h * D + d];
+                const int at = (d / DPT) * SEG + d % DPT;
+                sq[((size_t)buf * TB + tt) * RP + at] = q[(size_t)(t0 + tt) * ldq + (size_t)h * D + d];
+                sk[((size_t)buf * TB + tt) * RP + at] = k[(size_t)(t0 + tt) * ldk + (size_t)h * D + d];
             }
         }
-        for (int i = threadIdx.x; i < count * COLS; i += blockDim.x) {
-            const int tt = i / COLS, c = i % COLS;
-            sv[((size_t)buf * TB + tt) * COLS + c] = v0 + c < V ? to_float(v[(size_t)(t0 + tt) * ldv + (size_t)h * V + v0 + c]) : 0.f;
+        if (vec_v) {  // the CTA's 16 lanes of a token's values: four copies of 16 bytes, in flight with the rest
+            for (int i = threadIdx.x; i < count * (COLS / 4); i += blockDim.x) {
+                const int tt = i / (COLS / 4), c = (i % (COLS / 4)) * 4;
+                attn_cp16(sv + ((size_t)buf * TB + tt) * COLS + c, reinterpret_cast<const float*>(v) + (size_t)(t0 + tt) * ldv + (size_t)h * V + v0 + c);
+            }
+        } else {
+            for (int i = threadIdx.x; i < count * COLS; i += blockDim.x) {
+                const int tt = i / COLS, c = i % COLS;
+                sv[((size_t)buf * TB + tt) * COLS + c] = v0 + c < V ? to_float(v[(size_t)(t0 + tt) * ldv + (size_t)h * V + v0 + c]) : 0.f;
+            }
         }
         asm volatile("cp.async.commit_group;\n" ::);
     };
@@ -72,8 +84,9 @@ retention_scan_kernel(const float* __restrict__ q, int ldq, const float* __restr
     // lanes of q and k beyond D (the registers' room is a multiple of 8 * DPT) are zeros in both buffers
     for (int i = threadIdx.x; i < 2 * TB * (DS - D); i += blockDim.x) {
         const int row = i / (DS - D), d = D + i % (DS - D);
-        sq[(size_t)row * DS + d] = 0.f;
-        sk[(size_t)row * DS + d] = 0.f;
+        const int at = (d / DPT) * SEG + d % DPT;
+        sq[(size_t)row * RP + at] = 0.f;
+        sk[(size_t)row * RP + at] = 0.f;
     }
     for (int i = threadIdx.x; i < D * COLS; i += blockDim.x) {
         const int d = i / COLS, c = i % COLS;
@@ -93,17 +106,50 @@ retention_scan_kernel(const float* __restrict__ q, int ldq, const float* __restr
         __syncthreads();  // this block has landed, and everybody has left the other buffer
         if (t0 + TB < end) fetch(t0 + TB, buf ^ 1);
         const int count = min(TB, end - t0);
-        const float* bq = sq + (size_t)buf * TB * DS + sub * DPT;
-        const float* bk = sk + (size_t)buf * TB * DS + sub * DPT;
+        const float* bq = sq + (size_t)buf * TB * RP + sub * SEG;
+        const float* bk = sk + (size_t)buf * TB * RP + sub * SEG;
         const float* bv = sv + (size_t)buf * TB * COLS + col;
-#pragma unroll 4
-        for (int tt = 0; tt < count; ++tt) {
+        int tt = 0;
+        // eight tokens at a time: their partial sums are independent chains, and the eight lanes of a column then
+        // trade halves (4, 2, 1 values) so that lane `sub` ends with the whole sum of token tt + sub: 7 shuffles for
+        // 8 tokens, and every lane stores one value
+        for (; tt + 8 <= count; tt += 8) {
+            float o[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float vt = bv[(tt + u) * COLS];
+                float acc = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPT; i += 4) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(bk + (size_t)(tt + u) * RP + i);
+                    const float4 q4 = *reinterpret_cast<const float4*>(bq + (size_t)(tt + u) * RP + i);
+                    S[i] = fmaf(gamma, S[i], k4.x * vt);
+                    S[i + 1] = fmaf(gamma, S[i + 1], k4.y * vt);
+                    S[i + 2] = fmaf(gamma, S[i + 2], k4.z * vt);
+                    S[i + 3] = fmaf(gamma, S[i + 3], k4.w * vt);
+                    acc = fmaf(S[i], q4.x, acc);
+                    acc = fmaf(S[i + 1], q4.y, acc);
+                    acc = fmaf(S[i + 2], q4.z, acc);
+                    acc = fmaf(S[i + 3], q4.w, acc);
+                }
+                o[u] = acc;
+            }
+            const bool h4 = sub & 4, h2 = sub & 2, h1 = sub & 1;
+            float a[4], b[2];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) a[u] = (h4 ? o[u + 4] : o[u]) + __shfl_xor_sync(0xffffffffu, h4 ? o[u] : o[u + 4], 4);
+#pragma unroll
+            for (int u = 0; u < 2; ++u) b[u] = (h2 ? a[u + 2] : a[u]) + __shfl_xor_sync(0xffffffffu, h2 ? a[u] : a[u + 2], 2);
+            const float total = (h1 ? b[1] : b[0]) + __shfl_xor_sync(0xffffffffu, h1 ? b[0] : b[1], 1);
+            if (live) out[((size_t)(t0 + tt + sub) * H + h) * V + v0 + col] = total;
+        }
+        for (; tt < count; ++tt) {
             const float vt = bv[tt * COLS];
             float o = 0.f;
 #pragma unroll
             for (int i = 0; i < DPT; i += 4) {
-                const float4 k4 = *reinterpret_cast<const float4*>(bk + (size_t)tt * DS + i);
-                const float4 q4 = *reinterpret_cast<const float4*>(bq + (size_t)tt * DS + i);
+                const float4 k4 = *reinterpret_cast<const float4*>(bk + (size_t)tt * RP + i);
+                const float4 q4 = *reinterpret_cast<const float4*>(bq + (size_t)tt * RP + i);
                 S[i] = fmaf(gamma, S[i], k4.x * vt);
                 S[i + 1] = fmaf(gamma, S[i + 1], k4.y * vt);
                 S[i + 2] = fmaf(gamma, S[i + 2], k4.z * vt);
@@ -170,7 +216,7 @@ LLM_EXPORT int llm_retention_scan(const float* q, int ldq, const float* k, int l
     using bf = __nv_bfloat16;
     auto go = [&](auto kernel, auto* vp, int dpt, int tb) -> int {
         const int ds = dpt * TPC;
-        const size_t smem = ((size_t)ds * (COLS + 1) + (size_t)4 * tb * ds + (size_t)2 * tb * COLS) * sizeof(float);
+        const size_t smem = ((size_t)ds * (COLS + 1) + (size_t)4 * tb * (dpt + 4) * TPC + (size_t)2 * tb * COLS) * sizeof(float);
         if (smem > 48 * 1024) {
             const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;

@@ -14,19 +14,9 @@ namespace {
 //   w[t, e] = scale * s[e] (divided by the chosen scores' sum if renorm) for chosen experts, 0 for the others
 //   w[t, E] = sigmoid(z[t, E]) if shared_gate
 // w: [N, E + shared_gate] float32
-__global__ void __launch_bounds__(128)
-route_topk_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ correction, float* __restrict__ w, int N, int E,
-                  int top, float scale, int renorm, int shared_gate) {
-    extern __shared__ float sm[];  // per warp: s[E], choice[E]
-    pdl_trigger();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-    float* s = sm + (size_t)warp * 2 * E;
-    float* c = s + E;
-    pdl_wait();
-    if (t >= N) return;
-    const float* zr = z + (size_t)t * ldz;
-    float* wr = w + (size_t)t * (E + shared_gate);
+// One warp: from a token's logits zr[0 : E (+ 1)] to its row of weights wr; s, c: E floats of scratch each.
+__device__ __forceinline__ void route_row(const float* zr, const float* __restrict__ correction, float* wr, float* s, float* c, int E, int top,
+                                          float scale, int renorm, int shared_gate, int lane) {
     float m = -FLT_MAX;
     for (int e = lane; e < E; e += 32) m = fmaxf(m, zr[e]);
     m = warp_max(m);
@@ -69,6 +59,57 @@ route_topk_kernel(const float* __restrict__ z, int ldz, const float* __restrict_
     for (int e = lane; e < E; e += 32)
         if (wr[e] < 0.f) wr[e] = s[e] * f;
     if (shared_gate && lane == 0) wr[E] = 1.f / (1.f + expf(-zr[E]));
+}
+
+__global__ void __launch_bounds__(128)
+route_topk_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ correction, float* __restrict__ w, int N, int E,
+                  int top, float scale, int renorm, int shared_gate) {
+    extern __shared__ float sm[];  // per warp: s[E], choice[E]
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    float* s = sm + (size_t)warp * 2 * E;
+    pdl_wait();
+    if (t >= N) return;
+    route_row(z + (size_t)t * ldz, correction, w + (size_t)t * (E + shared_gate), s, s + E, E, top, scale, renorm, shared_gate, lane);
+}
+
+// The router's product and the choice in one kernel.  x: [N, K] (any type, read as 32-bit); wr: [E (+ 1), K] float32 (the last
+// row, if there is a shared gate, is the gate's); a CTA takes TT tokens: warp w sums up the logits of rows w, w + 8, ... for all of
+// them (a lane every 32nd element, then the lanes' sums: the same order whatever else is in the step), then a warp per token
+// chooses.
+template <typename TX, int TT>
+__global__ void __launch_bounds__(256)
+router_kernel(const TX* __restrict__ x, int ldx, const float* __restrict__ wr, const float* __restrict__ correction, float* __restrict__ out,
+              int N, int K, int E, int top, float scale, int renorm, int shared_gate) {
+    extern __shared__ float sm[];  // z[TT][rows], then per token s[E], c[E]
+    pdl_trigger();
+    const int rows = E + shared_gate, t0 = blockIdx.x * TT;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* z = sm;
+    pdl_wait();
+    for (int e = warp; e < rows; e += 8) {
+        float acc[TT];
+#pragma unroll
+        for (int tt = 0; tt < TT; ++tt) acc[tt] = 0.f;
+        const float* w = wr + (size_t)e * K;
+        for (int k = lane; k < K; k += 32) {
+            const float wv = w[k];
+#pragma unroll
+            for (int tt = 0; tt < TT; ++tt)
+                if (t0 + tt < N) acc[tt] = fmaf(wv, to_float(x[(size_t)(t0 + tt) * ldx + k]), acc[tt]);
+        }
+#pragma unroll
+        for (int tt = 0; tt < TT; ++tt) {
+            const float v = warp_sum(acc[tt]);
+            if (lane == 0) z[tt * rows + e] = v;
+        }
+    }
+    __syncthreads();
+    if (warp < TT && t0 + warp < N) {
+        float* s = sm + (size_t)TT * rows + (size_t)warp * 2 * E;
+        route_row(z + warp * rows, correction, out + (size_t)(t0 + warp) * rows, s, s + E, E, top, scale, renorm, shared_gate, lane);
+    }
 }
 
 __device__ __forceinline__ float activate(float v, int kind) {
@@ -152,6 +193,20 @@ LLM_EXPORT int llm_route_topk(const float* z, int ldz, const float* correction, 
     const size_t smem = (size_t)4 * 2 * E * sizeof(float);
     return launch_pdl(route_topk_kernel, dim3((N + 3) / 4), dim3(128), smem, stream, z, ldz, correction, w, N, E, top, scale, renorm,
                       shared_gate ? 1 : 0);
+}
+
+LLM_EXPORT int llm_router(const void* x, int x_dtype, int ldx, const float* wr, const float* correction, float* out, int N, int K, int E,
+                          int top, float scale, int renorm, int shared_gate, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (E <= 0 || top < 1 || top > E || E > 2048 || K <= 0) return LLM_ERR_BAD_ARGUMENT;
+    constexpr int TT = 4;
+    const int rows = E + (shared_gate ? 1 : 0);
+    const size_t smem = ((size_t)TT * rows + (size_t)TT * 2 * E) * sizeof(float);
+    const dim3 grid((N + TT - 1) / TT), block(256);
+    if (x_dtype == LLM_F32)
+        return launch_pdl(router_kernel<float, TT>, grid, block, smem, stream, (const float*)x, ldx, wr, correction, out, N, K, E, top, scale, renorm, shared_gate ? 1 : 0);
+    return launch_pdl(router_kernel<__nv_bfloat16, TT>, grid, block, smem, stream, (const __nv_bfloat16*)x, ldx, wr, correction, out, N, K, E, top, scale,
+                      renorm, shared_gate ? 1 : 0);
 }
 
 LLM_EXPORT int llm_expert_act_scale(const void* x, int ldx, const float* w, int ldw, void* y, int ldy, int dtype, int N, int C, int E,

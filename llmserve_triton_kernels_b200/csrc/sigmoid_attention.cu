@@ -130,7 +130,7 @@ sigmoid_attention_kernel(const TQ* __restrict__ q, int ldq, const TC* __restrict
 template <typename TO>
 __global__ void __launch_bounds__(256)
 sum_parts_kernel(const float* __restrict__ part, TO* __restrict__ out, const int* __restrict__ positions, int row, size_t count,
-                 int split_keys, int window) {
+                 int split_keys, int window, int shares) {
     pdl_trigger();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= count) return;
@@ -138,7 +138,9 @@ sum_parts_kernel(const float* __restrict__ part, TO* __restrict__ out, const int
     const int first = window > 0 ? max(0, pos - window + 1) : 0;
     pdl_wait();
     float s = 0.f;
-    for (int k = first / split_keys; k <= pos / split_keys; ++k) s += part[(size_t)k * count + i];
+    // stretch k lies in share k % shares; a token with more stretches than shares has keys in every share
+    const int k_lo = first / split_keys, k_hi = min(pos / split_keys, k_lo + shares - 1);
+    for (int k = k_lo; k <= k_hi; ++k) s += part[(size_t)(k % shares) * count + i];
     out[i] = from_float<TO>(s);
 }
 
@@ -264,18 +266,18 @@ LLM_EXPORT int llm_sigmoid_attention(const void* q, int q_dtype, int ldq, const 
     const size_t count = (size_t)N * H * V;
     const dim3 g2((unsigned)((count + 255) / 256));
     if (out_dtype == LLM_F32)
-        return launch_pdl(sum_parts_kernel<float>, g2, dim3(256), 0, stream, (const float*)parts, (float*)out, positions, H * V, count, split_keys, window);
-    return launch_pdl(sum_parts_kernel<bf>, g2, dim3(256), 0, stream, (const float*)parts, (bf*)out, positions, H * V, count, split_keys, window);
+        return launch_pdl(sum_parts_kernel<float>, g2, dim3(256), 0, stream, (const float*)parts, (float*)out, positions, H * V, count, split_keys, window, splits);
+    return launch_pdl(sum_parts_kernel<bf>, g2, dim3(256), 0, stream, (const float*)parts, (bf*)out, positions, H * V, count, split_keys, window, splits);
 }
 
 // out[t, :] = the sum of parts[s][t, :] over the stretches s in which token t has keys, in their order.
 LLM_EXPORT int llm_sigmoid_sum_parts(const float* parts, void* out, int out_dtype, const int* positions, int N, int row, int split_keys,
-                                     int window, cudaStream_t stream) {
+                                     int window, int shares, cudaStream_t stream) {
     if (N <= 0 || row <= 0) return 0;
     const size_t count = (size_t)N * row;
     const dim3 grid((unsigned)((count + 255) / 256));
-    if (out_dtype == LLM_F32) return launch_pdl(sum_parts_kernel<float>, grid, dim3(256), 0, stream, parts, (float*)out, positions, row, count, split_keys, window);
-    return launch_pdl(sum_parts_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, parts, (__nv_bfloat16*)out, positions, row, count, split_keys, window);
+    if (out_dtype == LLM_F32) return launch_pdl(sum_parts_kernel<float>, grid, dim3(256), 0, stream, parts, (float*)out, positions, row, count, split_keys, window, shares);
+    return launch_pdl(sum_parts_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, parts, (__nv_bfloat16*)out, positions, row, count, split_keys, window, shares);
 }
 
 // in_dtype: the projections' type; q_dtype: the queries' type on their way out; k_dtype: the keys' (and the pool's).

@@ -19,6 +19,8 @@ using namespace attn;
 constexpr int BM = 16;   // query tokens a CTA
 constexpr int HB = 16;   // output heads a CTA
 constexpr int THREADS = 512;
+constexpr int MAX_SHARES = 16;  // CTAs that share a tile's keys: stretch s goes to CTA s % 16, so that a step whose grid is made for the
+                                // longest context a pool allows does not launch hundreds of CTAs without keys
 
 struct SigMmaParams {
     const __nv_bfloat16* q;
@@ -28,7 +30,7 @@ struct SigMmaParams {
     int table_width;
     const float *bias, *mix;
     __nv_bfloat16* out;
-    float* parts;  // [splits][N][H * V] partial sums when the keys are shared out over several CTAs (else null)
+    float* parts;  // [grid.z][N][H * V] partial sums when the keys are shared out over several CTAs (else null)
     int N, R, H, KV, D, V, Dp, page_size, window, split_keys, splits;
     float scale, cap;
 };
@@ -56,7 +58,7 @@ sigmoid_attention_mma_kernel(const SigMmaParams p) {
     pdl_trigger();
     // which request and which of its tiles: the tiles of the requests lie one after the other
     if (tid == 0) {
-        int rest = blockIdx.x, r = 0;
+        int rest = gridDim.x - 1 - blockIdx.x, r = 0;  // the last tiles of a request see the most keys: they start first
         for (; r < p.R; ++r) {
             const int tiles = (p.cu_tokens[r + 1] - p.cu_tokens[r] + BM - 1) / BM;
             if (rest < tiles) break;
@@ -77,11 +79,15 @@ sigmoid_attention_mma_kernel(const SigMmaParams p) {
     const int pos0 = p.positions[t0];  // the tile's tokens stand at pos0, pos0 + 1, ...
     const int* table = p.page_table + (size_t)r * p.table_width;
     const size_t plane = (size_t)KV * p.page_size * p.Dp;
-    // the keys of this CTA: what any row of the tile sees, within this CTA's stretch
-    const int first = max(p.window > 0 ? max(0, pos0 - p.window + 1) : 0, split * p.split_keys);
-    const int last = min(pos0 + rows - 1, (split + 1) * p.split_keys - 1);
-    if (p.splits > 1 && first > last) return;  // the sum reads only the stretches in which a row has keys
-    const int j_begin = (first / BN) * BN;
+    // the keys that any row of the tile sees; this CTA takes the stretches split, split + gridDim.z, ... of them
+    const int tile_first = p.window > 0 ? max(0, pos0 - p.window + 1) : 0, tile_last = pos0 + rows - 1;
+    {
+        bool any = false;
+        for (int s = split; s < p.splits && !any; s += gridDim.z)
+            any = max(tile_first, s * p.split_keys) <= min(tile_last, (s + 1) * p.split_keys - 1);
+        if (!any) return;  // the sum reads only the partial sums of CTAs that had keys
+    }
+    int first = 0, last = -1;  // of the stretch at hand
     pdl_wait();
     // the tile's queries, every head: 16 bytes a thread and turn; rows beyond the request's tokens are zeros
     {
@@ -94,34 +100,27 @@ sigmoid_attention_mma_kernel(const SigMmaParams p) {
         }
     }
 
-    auto load_keys = [&](int j0) {
-        const int chunks = D / 8;
-        for (int i = tid; i < KV * BN * chunks; i += THREADS) {
-            const int ch = i % chunks, jj = (i / chunks) % BN, c = i / (chunks * BN);
+    // a thread copies the same 16 bytes of a key's row for every key/value head: one look at the page table a row
+    auto load_rows = [&](int j0, bf* dst, int pitch, int chunks, size_t second_plane) {
+        for (int i = tid; i < BN * chunks; i += THREADS) {
+            const int jj = i / chunks, ch = i - jj * chunks;
             const int j = j0 + jj;
             const bool ok = j <= last;
             const bf* src = p.pool;
-            if (ok) src += (size_t)table[j / p.page_size] * 2 * plane + ((size_t)c * p.page_size + j % p.page_size) * p.Dp + ch * 8;
-            cp_async16(sK + ((size_t)c * BN + jj) * DQ + ch * 8, src, ok);
+            if (ok) src += (size_t)table[j / p.page_size] * 2 * plane + second_plane + (size_t)(j % p.page_size) * p.Dp + ch * 8;
+            bf* to = dst + (size_t)jj * pitch + ch * 8;
+            for (int c = 0; c < KV; ++c) cp_async16(to + (size_t)c * BN * pitch, ok ? src + (size_t)c * p.page_size * p.Dp : src, ok);
         }
     };
-    auto load_values = [&](int j0) {
-        constexpr int chunks = V / 8;
-        for (int i = tid; i < KV * BN * chunks; i += THREADS) {
-            const int ch = i % chunks, jj = (i / chunks) % BN, c = i / (chunks * BN);
-            const int j = j0 + jj;
-            const bool ok = j <= last;
-            const bf* src = p.pool;
-            if (ok) src += (size_t)table[j / p.page_size] * 2 * plane + plane + ((size_t)c * p.page_size + j % p.page_size) * p.Dp + ch * 8;
-            cp_async16(sV + ((size_t)c * BN + jj) * VQ + ch * 8, src, ok);
-        }
-    };
+    auto load_keys = [&](int j0) { load_rows(j0, sK, DQ, D / 8, 0); };
+    auto load_values = [&](int j0) { load_rows(j0, sV, VQ, V / 8, plane); };
 
     float O[NV8][4];
 #pragma unroll
     for (int n = 0; n < NV8; ++n)
 #pragma unroll
         for (int e = 0; e < 4; ++e) O[n][e] = 0.f;
+    const float inv_cap = p.cap > 0.f ? 1.f / p.cap : 0.f;
     const int h_out = hb * HB + warp;          // the output head of this warp (phase 3)
     const bool has_out = warp < HB && h_out < H;
     const int c_out = has_out ? h_out / group : 0;
@@ -132,6 +131,11 @@ sigmoid_attention_mma_kernel(const SigMmaParams p) {
     const bool mixes = oct < 2;
     const bool mix_row = mixes && mi < rows;  // rows beyond the request's tokens keep weights of zero
 
+    for (int stretch = split; stretch < p.splits; stretch += gridDim.z) {
+    first = max(tile_first, stretch * p.split_keys);
+    last = min(tile_last, (stretch + 1) * p.split_keys - 1);
+    if (first > last) continue;
+    const int j_begin = (first / BN) * BN;
     load_keys(j_begin);
     load_values(j_begin);
     cp_async_commit();
@@ -158,24 +162,43 @@ sigmoid_attention_mma_kernel(const SigMmaParams p) {
                     mma_bf16(S[2 * np + 1], a, b[2], b[3]);
                 }
             }
+            // cap * tanh(x / cap) = cap * (1 - 2 / (1 + 2^(x c1))) with c1 = 2 log2(e) / cap, the sigmoid 1 / (1 + 2^(-y log2 e)):
+            // two ex2.approx and two rcp.approx a weight (relative error about 2^-22 each), everything else folded into constants
             const float bg = p.bias ? p.bias[g] : 0.f;
+            const float LOG2E = 1.4426950408889634f;
+            const float c1 = p.scale * 2.f * inv_cap * LOG2E, c2 = -p.scale * LOG2E, nb = -bg * LOG2E, ncap = -p.cap * LOG2E;
 #pragma unroll
-            for (int n = 0; n < BN / 8; ++n)
+            for (int half = 0; half < 2; ++half) {
+                const int i = (lane >> 2) + half * 8;
+                const int pos = pos0 + i;
+                const int hi = i < rows ? min(pos, last) : -1;
+                const int lo = max(p.window > 0 ? max(0, pos - p.window + 1) : 0, first);
+                if (hi < max(lo, j0)) {  // a row without a key in this tile (one beyond the request's tokens, as most rows of a decode step's tile)
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const int i = (lane >> 2) + half * 8;
-                    const int pos = pos0 + i;
-                    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+                    for (int n = 0; n < BN / 8; ++n)
+                        *reinterpret_cast<float2*>(sP + ((size_t)g * BM + i) * PP + n * 8 + (lane & 3) * 2) = make_float2(0.f, 0.f);
+                    continue;
+                }
+#pragma unroll
+                for (int n = 0; n < BN / 8; ++n) {
                     float w2[2];
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int j = j0 + n * 8 + (lane & 3) * 2 + e;
-                        float s = S[n][half * 2 + e] * p.scale;
-                        if (p.cap > 0.f) s = p.cap * tanhf(s / p.cap);
-                        w2[e] = (i < rows && j <= min(pos, last) && j >= max(lo, first)) ? 1.f / (1.f + expf(-(s + bg))) : 0.f;
+                        const float sc = S[n][half * 2 + e];
+                        float y;  // -(capped score + bias) * log2(e)
+                        if (p.cap > 0.f) {
+                            const float t = 1.f - __fdividef(2.f, 1.f + fast_exp2(fminf(sc * c1, 100.f)));
+                            y = fmaf(ncap, t, nb);
+                        } else {
+                            y = fmaf(sc, c2, nb);
+                        }
+                        const float w = __fdividef(1.f, 1.f + fast_exp2(fminf(y, 100.f)));
+                        w2[e] = (j <= hi && j >= lo) ? w : 0.f;
                     }
                     *reinterpret_cast<float2*>(sP + ((size_t)g * BM + i) * PP + n * 8 + (lane & 3) * 2) = make_float2(w2[0], w2[1]);
                 }
+            }
         }
         __syncthreads();  // (B) every head's weights are in shared memory; nobody reads the keys any more
         if (j0 + BN <= last) load_keys(j0 + BN);
@@ -227,6 +250,7 @@ sigmoid_attention_mma_kernel(const SigMmaParams p) {
         cp_async_commit();
     }
     cp_async_wait<0>();
+    }  // stretches
     if (!has_out) return;
 #pragma unroll
     for (int n = 0; n < NV8; ++n)
@@ -249,7 +273,7 @@ int launch(const SigMmaParams& p, int tiles, size_t smem, cudaStream_t stream) {
         const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    return launch_pdl(kernel, dim3(tiles, (p.H + HB - 1) / HB, p.splits), dim3(THREADS), smem, stream, p);
+    return launch_pdl(kernel, dim3(tiles, (p.H + HB - 1) / HB, p.splits < MAX_SHARES ? p.splits : MAX_SHARES), dim3(THREADS), smem, stream, p);
 }
 
 size_t smem_bytes(int H, int KV, int D, int V, int BN) {
@@ -262,8 +286,8 @@ size_t smem_bytes(int H, int KV, int D, int V, int BN) {
 
 // `tiles`: the sum over the requests of ceil(tokens / 16).  Returns LLM_ERR_UNSUPPORTED for sizes it does not take
 // (lanes that are no multiples of 16, values wider than 128 lanes, heads that do not fit the shared memory).
-// `splits` > 1: the keys are shared out in stretches of `split_keys` (a multiple of 32) and the partial sums left in
-// `parts [splits][N][H * V]` for llm_sigmoid_sum_parts.
+// `splits` > 1: the keys are shared out in stretches of `split_keys` (a multiple of 32), stretch s to share s % shares with
+// shares = min(splits, 16), and the partial sums left in `parts [shares][N][H * V]` for llm_sigmoid_sum_parts.
 LLM_EXPORT int llm_sigmoid_attention_mma(const void* q, int ldq, const void* pool, const int* page_table, int table_width,
                                          const int* positions, const int* cu_tokens, const float* bias, const float* mix, void* out,
                                          float* parts, int tiles, int N, int R, int H, int KV, int D, int V, int Dp, int page_size,

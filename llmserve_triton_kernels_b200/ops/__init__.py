@@ -60,10 +60,11 @@ _SIGNATURES = {
     "llm_sigmoid_attention": [_vp, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i,
                               _i, _i, _vp],
     "llm_sigmoid_attention_mma": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i, _i, _vp],
-    "llm_sigmoid_sum_parts": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
+    "llm_sigmoid_sum_parts": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
     "llm_qk_prepare": [_vp, _i, _i, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _f, _vp, _i, _vp, _f, _i, _i, _i, _i, _i, _vp],
     "llm_retention_scan": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "llm_head_norm_gate": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _i, _vp],
+    "llm_router": [_vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
     "llm_route_topk": [_vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp],
     "llm_expert_act_scale": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "llm_branch_norm_sum": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _f, _f, _vp],
@@ -1150,8 +1151,9 @@ def biased_paged_attention(qkv: torch.Tensor, pool: torch.Tensor, page_table: to
 # Operations of layers whose attention weighs keys by a sigmoid and mixes the heads' weights, that keep a decaying
 # matrix of state per head, that route tokens to a few of many small feed-forward layers, or that run mixers side by
 # side (csrc/sigmoid_attention.cu, retention.cu, routing.cu).
-_SIGMOID_SPLIT_KEYS = 256  # a stretch of keys that one CTA sums up when a context is shared out
+_SIGMOID_SPLIT_KEYS = 128  # a stretch of keys that one CTA sums up when a context is shared out
 _SIGMOID_SPLIT_MAX_TOKENS = 64  # steps of more tokens have CTAs enough without cutting the keys
+_SIGMOID_SHARES = 16  # the tensor-core kernel's CTAs per tile of tokens: stretch s of the keys goes to share s % 16
 
 
 def qk_prepare(proj: torch.Tensor, positions: torch.Tensor | None, *, heads: int, kv_heads: int, dim: int, value_dim: int = 0,
@@ -1227,7 +1229,8 @@ def sigmoid_attention(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Ten
             _check(code, "sigmoid_attention (tensor cores)")
             if splits > 1:
                 _check(_launch("llm_sigmoid_sum_parts", _ptr(parts), _ptr(out), _code(out.dtype), _ptr(ctx.positions), n,
-                               num_heads * value_dim, split_keys, int(window or 0), _stream()), "sigmoid_attention (sum of the stretches)")
+                               num_heads * value_dim, split_keys, int(window or 0), min(splits, _SIGMOID_SHARES), _stream()),
+                       "sigmoid_attention (sum of the stretches)")
             return out
         add_launches(-1)  # sizes the kernel does not take: the general one below
     code = _launch(
@@ -1288,6 +1291,22 @@ def route_topk(z: torch.Tensor, correction: torch.Tensor | None, experts: int, t
     code = _launch("llm_route_topk", _ptr(z), z.stride(0), _ptr(correction), _ptr(out), z.shape[0], experts, top, float(scale),
                    int(renormalize), int(shared_gate), _stream())
     _check(code, "route_topk")
+    return out
+
+
+def route(x: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor | None, experts: int, top: int, scale: float = 1.0,
+          renormalize: bool = False, shared_gate: bool = False) -> torch.Tensor:
+    """The router's 32-bit product and :func:`route_topk` in one kernel: ``x [N, K]`` (float32 or bfloat16, read as 32-bit),
+    ``w_router [experts (+ 1), K]`` float32 (its last row the shared expert's gate with ``shared_gate``).  A token's sums
+    are added in an order of their own, whatever else the step holds.  Returns ``[N, experts (+ 1)]`` float32."""
+    rows = experts + int(shared_gate)
+    _need(x.dim() == 2 and x.stride(1) == 1 and w_router.dtype == torch.float32 and w_router.is_contiguous()
+          and tuple(w_router.shape) == (rows, x.shape[1]), "route: x [N, K], w_router float32 [experts (+ 1), K]")
+    _need(correction is None or (correction.dtype == torch.float32 and correction.is_contiguous() and correction.numel() == experts), "route: correction is float32 [experts]")
+    out = torch.empty((x.shape[0], rows), dtype=torch.float32, device=x.device)
+    code = _launch("llm_router", _ptr(x), _code(x.dtype), x.stride(0), _ptr(w_router), _ptr(correction), _ptr(out), x.shape[0], x.shape[1],
+                   experts, top, float(scale), int(renormalize), int(shared_gate), _stream())
+    _check(code, "route")
     return out
 
 

@@ -25,6 +25,10 @@ class PreNormBlock(Block):
         self.ff_norm = ff_norm
         self.feed_forward = feed_forward
         self.residual_scale = float(residual_scale)  # x += residual_scale * part(norm(x))
+        # whether the part behind each norm takes the stream in factored form (ops.NormedInput); where it does not, the
+        # product in front of the norm is not asked for that form (it would only be multiplied out again)
+        mixer_norm.feeds_factored = bool(getattr(mixer, "accepts_sink", False))
+        ff_norm.feeds_factored = bool(getattr(feed_forward, "accepts_sink", False))
 
     @property
     def graph_safe(self) -> bool:
@@ -70,6 +74,8 @@ class PreNormBlock(Block):
         weight, eps = fused() if fused is not None else (None, 0.0)
         if self.residual_scale != 1.0:
             weight = None  # the product that also normalises adds its result unscaled
+        if not getattr(norm, "feeds_factored", True):
+            weight = None  # whoever reads that norm wants a plain tensor: the product only adds, the norm runs as a kernel
         return ops.ResidualSink(resid, weight, eps, norm, alpha=self.residual_scale)
 
 
@@ -82,6 +88,7 @@ class MixerOnlyBlock(PreNormBlock):
         self.mixer_norm = mixer_norm
         self.mixer = mixer
         self.residual_scale = float(residual_scale)
+        mixer_norm.feeds_factored = bool(getattr(mixer, "accepts_sink", False))
 
     @property
     def graph_safe(self) -> bool:

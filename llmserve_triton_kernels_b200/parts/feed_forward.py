@@ -119,7 +119,8 @@ class RoutedMLP(FeedForward):
     ``shared.up``, ``shared.down``, ``shared.sg``.
 
     All experts' up matrices are stacked (the shared expert's last), so are the down matrices side by side: a step is
-    two matrix products over every expert with, between them, one kernel that applies the activation and the token's
+    one kernel for the router (its 32-bit product and the choice) and two matrix products over every expert with, between
+    them, one kernel that applies the activation and the token's
     weight of each expert's block of columns (0 for an expert the token did not choose, the gate for the shared one).
     The second product then sums over the experts by itself.  Every weight matrix is read once a step whatever the
     tokens chose, which is what a decode step of several requests costs anyway; a prompt pays the products of the
@@ -170,8 +171,7 @@ class RoutedMLP(FeedForward):
 
     def forward(self, x, ctx, sink=None):
         xt = x.materialize() if isinstance(x, ops.NormedInput) else x
-        z = ops.linear(xt if xt.dtype == torch.float32 else xt.float(), self.w_router)
-        weights = ops.route_topk(z, self.correction, self.experts, self.top, self.router_scale, self.renormalize, self.shared_gate)
+        weights = ops.route(xt, self.w_router, self.correction, self.experts, self.top, self.router_scale, self.renormalize, self.shared_gate)
         if self.shared_size and not self.shared_gate:
             weights = torch.cat((weights, torch.ones_like(weights[:, :1])), dim=1)
         act = ops.expert_act_scale(ops.linear(xt, self.w_up), weights, self.experts, self.expert_size, self.activation)

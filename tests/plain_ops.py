@@ -396,6 +396,10 @@ def route_topk(z, correction, experts, top, scale=1.0, renormalize=False, shared
     return w
 
 
+def route(x, w_router, correction, experts, top, scale=1.0, renormalize=False, shared_gate=False):
+    return route_topk(x.float() @ w_router.float().t(), correction, experts, top, scale, renormalize, shared_gate)
+
+
 def expert_act_scale(x, weights, experts, ff, activation):
     y = unary(x.float(), activation)
     cols = torch.arange(x.shape[1], device=x.device)
@@ -416,6 +420,7 @@ ALL = (
     "retention_scan",
     "head_norm_gate",
     "route_topk",
+    "route",
     "expert_act_scale",
     "branch_norm_sum",
     "group_rmsnorm",

@@ -172,6 +172,16 @@ def test_routing_and_expert_weights(E, top, ff, shared):
     big[0] = 10.0
     w = ops.route_topk(z, big, E, top, 1.0, False, False)
     close(w[:, 0], torch.softmax(z[:, :E], -1)[:, 0], 1e-5, "the chosen expert's weight is its score")
+    # the router's product and the choice in one kernel, from 32-bit and from bfloat16 rows with a pitch
+    for K in (40, 256):
+        wr = torch.randn(E + 1, K, device=DEV)
+        for dtype in (torch.float32, torch.bfloat16):
+            h = torch.randn(N, K + 8, device=DEV).to(dtype)[:, :K]
+            zz = h.float() @ wr.t()
+            margin = (zz[:, :E].softmax(-1) + corr).sort(-1).values
+            sure = (margin[:, 1:] - margin[:, :-1]).min(-1).values > 1e-4 if E > 1 else torch.ones(N, dtype=torch.bool, device=DEV)
+            got, ref = ops.route(h, wr, corr, E, top, 2.5, False, True), plain_ops.route(h, wr, corr, E, top, 2.5, False, True)
+            close(got[sure], ref[sure], 1e-4, f"route K={K} {dtype}")
     for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
         x = torch.randn(N, E * ff + shared, device=DEV).to(dtype)
         w = plain_ops.route_topk(z, corr, E, top, 2.5, False, True)
