@@ -451,11 +451,11 @@ def _kafepel_kernels(design, twin, ops, torch, timed, ctx_for, i32, hbm, tensor,
         hbm(f"llama_rmsnorm_{label}", us, n * width * (4 + 4 + 4 + 2))
         # routed feed-forward: the choice, and the activation with the tokens' weights
         E, top, eff, sff = moe["router"]["experts"], moe["router"]["top"], moe["expert"]["ff"], moe["shared"]["ff"]
-        z = torch.randn(n, E + 1, device=device)
+        hx, wr = torch.randn(n, width, device=device).to(bf), torch.randn(E + 1, width, device=device)
         corr = torch.zeros(E, device=device)
-        us = timed(lambda: ops.route_topk(z, corr, E, top, 2.5, False, True))
-        hbm(f"route_topk_{label}", us, n * (2 * E + 2) * 4, like="(no like kernel in Llama)")
-        weights = ops.route_topk(z, corr, E, top, 2.5, False, True)
+        us = timed(lambda: ops.route(hx, wr, corr, E, top, 2.5, False, True))
+        hbm(f"router_{label}", us, n * width * 2 + (E + 1) * width * 4 + n * (E + 1) * 4, like="(no like kernel in Llama)")
+        weights = ops.route(hx, wr, corr, E, top, 2.5, False, True)
         up = torch.randn(n, E * eff + sff, device=device).to(bf)
         us = timed(lambda: ops.expert_act_scale(up, weights, E, eff, "relu2"))
         hbm(f"expert_act_scale_{label}", us, n * (E * eff + sff) * 4, like="llama_swiglu")

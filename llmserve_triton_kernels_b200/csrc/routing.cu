@@ -191,6 +191,10 @@ LLM_EXPORT int llm_route_topk(const float* z, int ldz, const float* correction, 
     if (N <= 0) return 0;
     if (E <= 0 || top < 1 || top > E || E > 4096 || ldz < E + (shared_gate ? 1 : 0)) return LLM_ERR_BAD_ARGUMENT;
     const size_t smem = (size_t)4 * 2 * E * sizeof(float);
+    if (smem > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(route_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
     return launch_pdl(route_topk_kernel, dim3((N + 3) / 4), dim3(128), smem, stream, z, ldz, correction, w, N, E, top, scale, renorm,
                       shared_gate ? 1 : 0);
 }
@@ -203,6 +207,11 @@ LLM_EXPORT int llm_router(const void* x, int x_dtype, int ldx, const float* wr, 
     const int rows = E + (shared_gate ? 1 : 0);
     const size_t smem = ((size_t)TT * rows + (size_t)TT * 2 * E) * sizeof(float);
     const dim3 grid((N + TT - 1) / TT), block(256);
+    if (smem > 48 * 1024) {
+        const cudaError_t e = x_dtype == LLM_F32 ? cudaFuncSetAttribute(router_kernel<float, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                                                 : cudaFuncSetAttribute(router_kernel<__nv_bfloat16, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
     if (x_dtype == LLM_F32)
         return launch_pdl(router_kernel<float, TT>, grid, block, smem, stream, (const float*)x, ldx, wr, correction, out, N, K, E, top, scale, renorm, shared_gate ? 1 : 0);
     return launch_pdl(router_kernel<__nv_bfloat16, TT>, grid, block, smem, stream, (const __nv_bfloat16*)x, ldx, wr, correction, out, N, K, E, top, scale,

@@ -101,7 +101,7 @@ sigmoid_attention_mma_kernel(const SigMmaParams p) {
     }
 
     // a thread copies the same 16 bytes of a key's row for every key/value head: one look at the page table a row
-    auto load_rows = [&](int j0, bf* dst, int pitch, int chunks, size_t second_plane) {
+    auto load_rows = [&](int j0, bf* dst, int pitch, int chunks, size_t second_plane, int c_lo, int c_hi) {
         for (int i = tid; i < BN * chunks; i += THREADS) {
             const int jj = i / chunks, ch = i - jj * chunks;
             const int j = j0 + jj;
@@ -109,11 +109,13 @@ sigmoid_attention_mma_kernel(const SigMmaParams p) {
             const bf* src = p.pool;
             if (ok) src += (size_t)table[j / p.page_size] * 2 * plane + second_plane + (size_t)(j % p.page_size) * p.Dp + ch * 8;
             bf* to = dst + (size_t)jj * pitch + ch * 8;
-            for (int c = 0; c < KV; ++c) cp_async16(to + (size_t)c * BN * pitch, ok ? src + (size_t)c * p.page_size * p.Dp : src, ok);
+            for (int c = c_lo; c <= c_hi; ++c) cp_async16(to + (size_t)c * BN * pitch, ok ? src + (size_t)c * p.page_size * p.Dp : src, ok);
         }
     };
-    auto load_keys = [&](int j0) { load_rows(j0, sK, DQ, D / 8, 0); };
-    auto load_values = [&](int j0) { load_rows(j0, sV, VQ, V / 8, plane); };
+    // keys of every key/value head (the scores of all heads are wanted); values only of the heads behind this CTA's output heads
+    const int v_lo = (hb * HB) / group, v_hi = min(H - 1, hb * HB + HB - 1) / group;
+    auto load_keys = [&](int j0) { load_rows(j0, sK, DQ, D / 8, 0, 0, KV - 1); };
+    auto load_values = [&](int j0) { load_rows(j0, sV, VQ, V / 8, plane, v_lo, v_hi); };
 
     float O[NV8][4];
 #pragma unroll
