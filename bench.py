@@ -438,7 +438,7 @@ def _kafepel_kernels(design, twin, ops, torch, timed, ctx_for, i32, hbm, tensor,
         rv = torch.randn(n, RH * RV, device=device)
         decay = torch.tensor(R["decay"], dtype=torch.float32, device=device)
         states, sl = torch.zeros(8, RH, RD, RV, device=device), i32(list(range(len(qs))))
-        us = timed(lambda: ops.retention_scan(rq, rk, rv, decay, states, sl, ctx.cu_tokens, len(qs), RH, RD, RV))
+        us = timed(lambda: ops.retention_scan(rq, rk, rv, decay, states, sl, ctx.cu_tokens, len(qs), RH, RD, RV, max(qs)))
         hbm(f"retention_scan_{label}", us, n * RH * (2 * RD + 2 * RV) * 4 + 2 * len(qs) * RH * RD * RV * 4, like="(no like kernel in Llama)")
         o, gate = torch.randn(n, RH, RV, device=device), torch.randn(n, RH * RV, device=device)
         us = timed(lambda: ops.head_norm_gate(o, gate, 1e-6, "silu", bf))

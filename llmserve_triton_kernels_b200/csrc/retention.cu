@@ -25,11 +25,25 @@ __device__ __forceinline__ void attn_cp16(float* smem, const float* gmem) {
 // values), the next block on its way (cp.async) while one is walked; thread (column, part) holds rows
 // part * DPT .. part * DPT + DPT - 1 of its column.  Only S is carried from token to token: the sums o_t of
 // neighbouring tokens overlap.
-template <typename TV, int DPT, int TB>
+//
+// Long requests are shared out over NS CTAs, each a stretch of the request's tokens (see stretch_of).  The recurrence is
+// linear in S, so a stretch can be walked from a zero state: its outputs then lack decay^(t - b + 1) S_b^T q_t, where S_b is
+// the state at the stretch's start b, and its end state lacks decay^(length) S_b.  Three launches: this kernel over all
+// stretches (the first from the slot's state, the others from zero; end states to `ends`), retention_starts_kernel
+// (the start state of every stretch, and the slot's new state), and this kernel once more with CORRECT (S = the start
+// state, held still; the missing term is added to the outputs).  NS == 1: one launch, as described above.
+__device__ __forceinline__ void stretch_of(int begin, int end, int s, int NS, int& b, int& e) {
+    const int length = ((end - begin + NS - 1) / NS + 7) & ~7;  // whole turns of eight tokens
+    b = min(end, begin + s * length);
+    e = min(end, b + length);
+}
+
+template <typename TV, int DPT, int TB, bool CORRECT>
 __global__ void __launch_bounds__(COLS * TPC)
 retention_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk, const TV* __restrict__ v, int ldv,
                       const float* __restrict__ decay, float* __restrict__ states, const int* __restrict__ state_slots,
-                      const int* __restrict__ cu_tokens, float* __restrict__ out, int H, int D, int V) {
+                      const int* __restrict__ cu_tokens, float* __restrict__ out, int H, int D, int V, int NS,
+                      float* __restrict__ ends, const float* __restrict__ starts) {
     constexpr int DS = DPT * TPC;   // rows of the state that the CTA's registers have room for (>= D)
     constexpr int SEG = DPT + 4;    // a part's lanes of a token's q or k, then 4 floats of room: the parts' 16-byte reads fall
     constexpr int RP = SEG * TPC;   // into different banks; RP: the pitch of a token's row
@@ -39,11 +53,20 @@ retention_scan_kernel(const float* __restrict__ q, int ldq, const float* __restr
     float* sk = sq + 2 * TB * RP;               // [2][TB][RP]
     float* sv = sk + 2 * TB * RP;               // [2][TB][COLS]
     pdl_trigger();
-    const int r = blockIdx.z, h = blockIdx.y, v0 = blockIdx.x * COLS;
+    const int r = blockIdx.z / NS, stretch = blockIdx.z % NS, h = blockIdx.y, v0 = blockIdx.x * COLS;
     const int sub = threadIdx.x % TPC, col = threadIdx.x / TPC;
-    const int begin = cu_tokens[r], end = cu_tokens[r + 1], slot = state_slots[r];
+    if (CORRECT && stretch == 0) return;  // the first stretch started from the true state
+    int begin, end;
+    stretch_of(cu_tokens[r], cu_tokens[r + 1], stretch, NS, begin, end);
+    const int slot = state_slots[r];
     const float gamma = decay[h];
-    float* state = states + ((size_t)slot * H + h) * D * V;
+    const float log2_gamma = log2f(gamma);
+    // where the state comes from and goes to
+    const size_t per_head = (size_t)D * V;
+    const float* state_in = CORRECT ? starts + ((size_t)(r * NS + stretch) * H + h) * per_head
+                                    : (stretch == 0 ? states + ((size_t)slot * H + h) * per_head : nullptr);
+    float* state_out = CORRECT ? nullptr : (NS > 1 ? ends + ((size_t)(r * NS + stretch) * H + h) * per_head : states + ((size_t)slot * H + h) * per_head);
+    if (CORRECT && begin >= end) return;
     const bool vec = (D % 4 == 0) && (ldq % 4 == 0) && (ldk % 4 == 0) && ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k)) % 16 == 0);  // rows of q and k may be copied 16 bytes at a time
     pdl_wait();
 
@@ -56,17 +79,18 @@ retention_scan_kernel(const float* __restrict__ q, int ldq, const float* __restr
                 const int tt = i / chunks, d = (i % chunks) * 4;
                 const int at = (d / DPT) * SEG + d % DPT;
                 attn_cp16(sq + ((size_t)buf * TB + tt) * RP + at, q + (size_t)(t0 + tt) * ldq + (size_t)h * D + d);
-                attn_cp16(sk + ((size_t)buf * TB + tt) * RP + at, k + (size_t)(t0 + tt) * ldk + (size_t)h * D + d);
+                if (!CORRECT) attn_cp16(sk + ((size_t)buf * TB + tt) * RP + at, k + (size_t)(t0 + tt) * ldk + (size_t)h * D + d);
             }
         } else {
             for (int i = threadIdx.x; i < count * D; i += blockDim.x) {
                 const int tt = i / D, d = i % D;
                 const int at = (d / DPT) * SEG + d % DPT;
                 sq[((size_t)buf * TB + tt) * RP + at] = q[(size_t)(t0 + tt) * ldq + (size_t)h * D + d];
-                sk[((size_t)buf * TB + tt) * RP + at] = k[(size_t)(t0 + tt) * ldk + (size_t)h * D + d];
+                if (!CORRECT) sk[((size_t)buf * TB + tt) * RP + at] = k[(size_t)(t0 + tt) * ldk + (size_t)h * D + d];
             }
         }
-        if (vec_v) {  // the CTA's 16 lanes of a token's values: four copies of 16 bytes, in flight with the rest
+        if (CORRECT) {
+        } else if (vec_v) {  // the CTA's 16 lanes of a token's values: four copies of 16 bytes, in flight with the rest
             for (int i = threadIdx.x; i < count * (COLS / 4); i += blockDim.x) {
                 const int tt = i / (COLS / 4), c = (i % (COLS / 4)) * 4;
                 attn_cp16(sv + ((size_t)buf * TB + tt) * COLS + c, reinterpret_cast<const float*>(v) + (size_t)(t0 + tt) * ldv + (size_t)h * V + v0 + c);
@@ -90,7 +114,7 @@ retention_scan_kernel(const float* __restrict__ q, int ldq, const float* __restr
     }
     for (int i = threadIdx.x; i < D * COLS; i += blockDim.x) {
         const int d = i / COLS, c = i % COLS;
-        tile[d * (COLS + 1) + c] = v0 + c < V ? state[(size_t)d * V + v0 + c] : 0.f;
+        tile[d * (COLS + 1) + c] = (state_in && v0 + c < V) ? state_in[(size_t)d * V + v0 + c] : 0.f;
     }
     __syncthreads();
     float S[DPT];
@@ -114,19 +138,23 @@ retention_scan_kernel(const float* __restrict__ q, int ldq, const float* __restr
         // trade halves (4, 2, 1 values) so that lane `sub` ends with the whole sum of token tt + sub: 7 shuffles for
         // 8 tokens, and every lane stores one value
         for (; tt + 8 <= count; tt += 8) {
+            float* mine = out + ((size_t)(t0 + tt + sub) * H + h) * V + v0 + col;  // lane `sub` ends with token tt + sub
+            const float before = (CORRECT && live) ? *mine : 0.f;                   // asked for now, wanted at the turn's end
             float o[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                const float vt = bv[(tt + u) * COLS];
+                const float vt = CORRECT ? 0.f : bv[(tt + u) * COLS];
                 float acc = 0.f;
 #pragma unroll
                 for (int i = 0; i < DPT; i += 4) {
-                    const float4 k4 = *reinterpret_cast<const float4*>(bk + (size_t)(tt + u) * RP + i);
                     const float4 q4 = *reinterpret_cast<const float4*>(bq + (size_t)(tt + u) * RP + i);
-                    S[i] = fmaf(gamma, S[i], k4.x * vt);
-                    S[i + 1] = fmaf(gamma, S[i + 1], k4.y * vt);
-                    S[i + 2] = fmaf(gamma, S[i + 2], k4.z * vt);
-                    S[i + 3] = fmaf(gamma, S[i + 3], k4.w * vt);
+                    if (!CORRECT) {
+                        const float4 k4 = *reinterpret_cast<const float4*>(bk + (size_t)(tt + u) * RP + i);
+                        S[i] = fmaf(gamma, S[i], k4.x * vt);
+                        S[i + 1] = fmaf(gamma, S[i + 1], k4.y * vt);
+                        S[i + 2] = fmaf(gamma, S[i + 2], k4.z * vt);
+                        S[i + 3] = fmaf(gamma, S[i + 3], k4.w * vt);
+                    }
                     acc = fmaf(S[i], q4.x, acc);
                     acc = fmaf(S[i + 1], q4.y, acc);
                     acc = fmaf(S[i + 2], q4.z, acc);
@@ -141,19 +169,21 @@ retention_scan_kernel(const float* __restrict__ q, int ldq, const float* __restr
 #pragma unroll
             for (int u = 0; u < 2; ++u) b[u] = (h2 ? a[u + 2] : a[u]) + __shfl_xor_sync(0xffffffffu, h2 ? a[u] : a[u + 2], 2);
             const float total = (h1 ? b[1] : b[0]) + __shfl_xor_sync(0xffffffffu, h1 ? b[0] : b[1], 1);
-            if (live) out[((size_t)(t0 + tt + sub) * H + h) * V + v0 + col] = total;
+            if (live) *mine = CORRECT ? fmaf(total, exp2f((float)(t0 + tt + sub - begin + 1) * log2_gamma), before) : total;
         }
         for (; tt < count; ++tt) {
-            const float vt = bv[tt * COLS];
+            const float vt = CORRECT ? 0.f : bv[tt * COLS];
             float o = 0.f;
 #pragma unroll
             for (int i = 0; i < DPT; i += 4) {
-                const float4 k4 = *reinterpret_cast<const float4*>(bk + (size_t)tt * RP + i);
                 const float4 q4 = *reinterpret_cast<const float4*>(bq + (size_t)tt * RP + i);
-                S[i] = fmaf(gamma, S[i], k4.x * vt);
-                S[i + 1] = fmaf(gamma, S[i + 1], k4.y * vt);
-                S[i + 2] = fmaf(gamma, S[i + 2], k4.z * vt);
-                S[i + 3] = fmaf(gamma, S[i + 3], k4.w * vt);
+                if (!CORRECT) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(bk + (size_t)tt * RP + i);
+                    S[i] = fmaf(gamma, S[i], k4.x * vt);
+                    S[i + 1] = fmaf(gamma, S[i + 1], k4.y * vt);
+                    S[i + 2] = fmaf(gamma, S[i + 2], k4.z * vt);
+                    S[i + 3] = fmaf(gamma, S[i + 3], k4.w * vt);
+                }
                 o = fmaf(S[i], q4.x, o);
                 o = fmaf(S[i + 1], q4.y, o);
                 o = fmaf(S[i + 2], q4.z, o);
@@ -162,9 +192,14 @@ retention_scan_kernel(const float* __restrict__ q, int ldq, const float* __restr
             o += __shfl_xor_sync(0xffffffffu, o, 1);
             o += __shfl_xor_sync(0xffffffffu, o, 2);
             o += __shfl_xor_sync(0xffffffffu, o, 4);
-            if (sub == 0 && live) out[((size_t)(t0 + tt) * H + h) * V + v0 + col] = o;
+            if (sub == 0 && live) {
+                float* at = out + ((size_t)(t0 + tt) * H + h) * V + v0 + col;
+                if (CORRECT) *at += o * exp2f((float)(t0 + tt - begin + 1) * log2_gamma);
+                else *at = o;
+            }
         }
     }
+    if (CORRECT) return;
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
@@ -174,8 +209,30 @@ retention_scan_kernel(const float* __restrict__ q, int ldq, const float* __restr
     __syncthreads();
     for (int i = threadIdx.x; i < D * COLS; i += blockDim.x) {
         const int d = i / COLS, c = i % COLS;
-        if (v0 + c < V) state[(size_t)d * V + v0 + c] = tile[d * (COLS + 1) + c];
+        if (v0 + c < V) state_out[(size_t)d * V + v0 + c] = tile[d * (COLS + 1) + c];
     }
+}
+
+// From the stretches' end states (the first from the true state, the others from zero) to the state at every stretch's
+// start and the slot's new state:  start_1 = end_0;  start_(s+1) = decay^(length_s) start_s + end_s.  One thread an element.
+__global__ void __launch_bounds__(256)
+retention_starts_kernel(const float* __restrict__ ends, float* __restrict__ starts, float* __restrict__ states,
+                        const float* __restrict__ decay, const int* __restrict__ state_slots, const int* __restrict__ cu_tokens, int H,
+                        int per_head, int NS) {
+    pdl_trigger();
+    const int r = blockIdx.z, h = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    const float log2_gamma = log2f(decay[h]);
+    const int t_begin = cu_tokens[r], t_end = cu_tokens[r + 1], slot = state_slots[r];
+    pdl_wait();
+    if (i >= per_head) return;
+    float S = ends[((size_t)(r * NS) * H + h) * per_head + i];
+    for (int s = 1; s < NS; ++s) {
+        starts[((size_t)(r * NS + s) * H + h) * per_head + i] = S;
+        int b, e;
+        stretch_of(t_begin, t_end, s, NS, b, e);
+        S = fmaf(e > b ? exp2f((float)(e - b) * log2_gamma) : 1.f, S, ends[((size_t)(r * NS + s) * H + h) * per_head + i]);
+    }
+    states[((size_t)slot * H + h) * per_head + i] = S;
 }
 
 // out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * gate(g[t, h, :]), one warp per (token, head).
@@ -207,12 +264,17 @@ head_norm_gate_kernel(const float* __restrict__ o, const TG* __restrict__ g, int
 
 }  // namespace
 
+// `stretches` > 1: long requests shared out over that many CTAs each; `scratch` then holds 2 * requests * stretches * H * D * V floats.
 LLM_EXPORT int llm_retention_scan(const float* q, int ldq, const float* k, int ldk, const void* v, int v_dtype, int ldv,
                                   const float* decay, float* states, const int* state_slots, const int* cu_tokens, float* out,
-                                  int requests, int H, int D, int V, cudaStream_t stream) {
+                                  int requests, int H, int D, int V, int stretches, float* scratch, cudaStream_t stream) {
     if (requests <= 0) return 0;
-    if (H <= 0 || D <= 0 || V <= 0 || D > 256 || requests > 65535 || H > 65535) return LLM_ERR_BAD_ARGUMENT;
-    const dim3 grid((V + COLS - 1) / COLS, H, requests), block(COLS * TPC);
+    if (H <= 0 || D <= 0 || V <= 0 || D > 256 || H > 65535 || stretches < 1 || (stretches > 1 && !scratch) || (long long)requests * stretches > 65535)
+        return LLM_ERR_BAD_ARGUMENT;
+    const int NS = stretches;
+    const dim3 grid((V + COLS - 1) / COLS, H, requests * NS), block(COLS * TPC);
+    float* ends = scratch;
+    float* starts = scratch ? scratch + (size_t)requests * NS * H * D * V : nullptr;
     using bf = __nv_bfloat16;
     auto go = [&](auto kernel, auto* vp, int dpt, int tb) -> int {
         const int ds = dpt * TPC;
@@ -221,15 +283,21 @@ LLM_EXPORT int llm_retention_scan(const float* q, int ldq, const float* k, int l
             const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
         }
-        return launch_pdl(kernel, grid, block, smem, stream, q, ldq, k, ldk, vp, ldv, decay, states, state_slots, cu_tokens, out, H, D, V);
+        return launch_pdl(kernel, grid, block, smem, stream, q, ldq, k, ldk, vp, ldv, decay, states, state_slots, cu_tokens, out, H, D, V, NS, ends,
+                          (const float*)starts);
     };
-#define LLM_RET(DPT, TB) \
-    (v_dtype == LLM_F32 ? go(retention_scan_kernel<float, DPT, TB>, (const float*)v, DPT, TB) : go(retention_scan_kernel<bf, DPT, TB>, (const bf*)v, DPT, TB))
-    if (D <= 32) return LLM_RET(4, 32);
-    if (D <= 64) return LLM_RET(8, 32);
-    if (D <= 128) return LLM_RET(16, 16);
-    return LLM_RET(32, 8);
+#define LLM_RET2(DPT, TB, C) \
+    (v_dtype == LLM_F32 ? go(retention_scan_kernel<float, DPT, TB, C>, (const float*)v, DPT, TB) : go(retention_scan_kernel<bf, DPT, TB, C>, (const bf*)v, DPT, TB))
+#define LLM_RET(C) (D <= 32 ? LLM_RET2(4, 32, C) : D <= 64 ? LLM_RET2(8, 32, C) : D <= 128 ? LLM_RET2(16, 16, C) : LLM_RET2(32, 8, C))
+    int code = LLM_RET(false);
+    if (code != 0 || NS == 1) return code;
+    const int per_head = D * V;
+    code = launch_pdl(retention_starts_kernel, dim3((per_head + 255) / 256, H, requests), dim3(256), 0, stream, (const float*)ends, starts, states, decay,
+                      state_slots, cu_tokens, H, per_head, NS);
+    if (code != 0) return code;
+    return LLM_RET(true);
 #undef LLM_RET
+#undef LLM_RET2
 }
 
 LLM_EXPORT int llm_head_norm_gate(const float* o, const void* g, int g_dtype, int ldg, void* out, int out_dtype, int N, int heads,

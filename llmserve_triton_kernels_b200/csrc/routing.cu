@@ -75,11 +75,11 @@ route_topk_kernel(const float* __restrict__ z, int ldz, const float* __restrict_
 }
 
 // The router's product and the choice in one kernel.  x: [N, K] (any type, read as 32-bit); wr: [E (+ 1), K] float32 (the last
-// row, if there is a shared gate, is the gate's); a CTA takes TT tokens: warp w sums up the logits of rows w, w + 8, ... for all of
-// them (a lane every 32nd element, then the lanes' sums: the same order whatever else is in the step), then a warp per token
+// row, if there is a shared gate, is the gate's); a CTA takes TT tokens: warp w sums up the logits of rows w, w + warps, ... for all of
+// them (a lane its share of the elements, then the lanes' sums: the same order whatever else is in the step), then a warp per token
 // chooses.
 template <typename TX, int TT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 router_kernel(const TX* __restrict__ x, int ldx, const float* __restrict__ wr, const float* __restrict__ correction, float* __restrict__ out,
               int N, int K, int E, int top, float scale, int renorm, int shared_gate) {
     extern __shared__ float sm[];  // z[TT][rows], then per token s[E], c[E]
@@ -88,16 +88,37 @@ router_kernel(const TX* __restrict__ x, int ldx, const float* __restrict__ wr, c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* z = sm;
     pdl_wait();
-    for (int e = warp; e < rows; e += 8) {
+    const int warps = blockDim.x >> 5;
+    // four elements a lane and turn where rows allow 16-byte (weights) and 4-element (x) loads; the lanes' order of sums is fixed
+    const bool wide = K % 4 == 0 && ldx % 4 == 0 && reinterpret_cast<uintptr_t>(wr) % 16 == 0 && reinterpret_cast<uintptr_t>(x) % (4 * sizeof(TX)) == 0;
+    for (int e = warp; e < rows; e += warps) {
         float acc[TT];
 #pragma unroll
         for (int tt = 0; tt < TT; ++tt) acc[tt] = 0.f;
         const float* w = wr + (size_t)e * K;
-        for (int k = lane; k < K; k += 32) {
-            const float wv = w[k];
+        if (wide) {
+#pragma unroll 4
+            for (int k = lane * 4; k < K; k += 128) {
+                const float4 wv = *reinterpret_cast<const float4*>(w + k);
 #pragma unroll
-            for (int tt = 0; tt < TT; ++tt)
-                if (t0 + tt < N) acc[tt] = fmaf(wv, to_float(x[(size_t)(t0 + tt) * ldx + k]), acc[tt]);
+                for (int tt = 0; tt < TT; ++tt) {
+                    if (t0 + tt >= N) continue;
+                    float xv[4];
+                    load4(x + (size_t)(t0 + tt) * ldx + k, xv);
+                    acc[tt] = fmaf(wv.x, xv[0], acc[tt]);
+                    acc[tt] = fmaf(wv.y, xv[1], acc[tt]);
+                    acc[tt] = fmaf(wv.z, xv[2], acc[tt]);
+                    acc[tt] = fmaf(wv.w, xv[3], acc[tt]);
+                }
+            }
+        } else {
+#pragma unroll 4
+            for (int k = lane; k < K; k += 32) {
+                const float wv = w[k];
+#pragma unroll
+                for (int tt = 0; tt < TT; ++tt)
+                    if (t0 + tt < N) acc[tt] = fmaf(wv, to_float(x[(size_t)(t0 + tt) * ldx + k]), acc[tt]);
+            }
         }
 #pragma unroll
         for (int tt = 0; tt < TT; ++tt) {
@@ -165,21 +186,32 @@ struct Branches {
 };
 
 __global__ void __launch_bounds__(256)
-branch_norm_sum_kernel(Branches br, int count, float* __restrict__ out, int C, float eps, float factor) {
+branch_norm_sum_kernel(Branches br, int count, float* __restrict__ out, int C, float eps, float factor, int cached) {
+    extern __shared__ float rowbuf[];  // [count][C] when the rows fit (`cached`): every row is read from memory once
     __shared__ float scratch[33];
     pdl_trigger();
     pdl_wait();
     const size_t row = (size_t)blockIdx.x * C;
     float scale[4];
-    for (int b = 0; b < count; ++b) {
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        if (b >= count) break;
         float ss = 0.f;
-        for (int i = threadIdx.x; i < C; i += blockDim.x) { const float v = br.x[b][row + i]; ss = fmaf(v, v, ss); }
+        for (int i = threadIdx.x; i < C; i += blockDim.x) {
+            const float v = br.x[b][row + i];
+            if (cached) rowbuf[b * C + i] = v;
+            ss = fmaf(v, v, ss);
+        }
         ss = block_sum(ss, scratch);
         scale[b] = 1.f / sqrtf(ss / (float)C + eps);
     }
     for (int i = threadIdx.x; i < C; i += blockDim.x) {
         float s = 0.f;
-        for (int b = 0; b < count; ++b) s += br.x[b][row + i] * scale[b] * br.w[b][i];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            if (b >= count) break;
+            s += (cached ? rowbuf[b * C + i] : br.x[b][row + i]) * scale[b] * br.w[b][i];
+        }
         out[row + i] = s * factor;
     }
 }
@@ -206,7 +238,9 @@ LLM_EXPORT int llm_router(const void* x, int x_dtype, int ldx, const float* wr, 
     constexpr int TT = 4;
     const int rows = E + (shared_gate ? 1 : 0);
     const size_t smem = ((size_t)TT * rows + (size_t)TT * 2 * E) * sizeof(float);
-    const dim3 grid((N + TT - 1) / TT), block(256);
+    const int rows_all = E + (shared_gate ? 1 : 0);
+    const int warps = rows_all < 8 ? 8 : rows_all > 32 ? 32 : rows_all;  // a warp a row of the router where they fit
+    const dim3 grid((N + TT - 1) / TT), block(32 * warps);
     if (smem > 48 * 1024) {
         const cudaError_t e = x_dtype == LLM_F32 ? cudaFuncSetAttribute(router_kernel<float, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
                                                  : cudaFuncSetAttribute(router_kernel<__nv_bfloat16, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -244,5 +278,11 @@ LLM_EXPORT int llm_branch_norm_sum(const float* x0, const float* w0, const float
     if (N <= 0) return 0;
     if (count < 1 || count > 4 || C <= 0) return LLM_ERR_BAD_ARGUMENT;
     Branches br = {{x0, x1, x2, x3}, {w0, w1, w2, w3}};
-    return launch_pdl(branch_norm_sum_kernel, dim3(N), dim3(256), 0, stream, br, count, out, C, eps, factor);
+    const size_t need = (size_t)count * C * sizeof(float);
+    const int cached = need <= 96 * 1024;
+    if (cached && need > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(branch_norm_sum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return launch_pdl(branch_norm_sum_kernel, dim3(N), dim3(256), cached ? need : 0, stream, br, count, out, C, eps, factor, cached);
 }

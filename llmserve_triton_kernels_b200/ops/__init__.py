@@ -62,7 +62,7 @@ _SIGNATURES = {
     "llm_sigmoid_attention_mma": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i, _i, _vp],
     "llm_sigmoid_sum_parts": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
     "llm_qk_prepare": [_vp, _i, _i, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _f, _vp, _i, _vp, _f, _i, _i, _i, _i, _i, _vp],
-    "llm_retention_scan": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "llm_retention_scan": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "llm_head_norm_gate": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _i, _vp],
     "llm_router": [_vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
     "llm_route_topk": [_vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp],
@@ -1244,12 +1244,18 @@ def sigmoid_attention(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Ten
     return out
 
 
+_RETENTION_MIN_STRETCH = 64  # tokens a stretch of a long request has at least
+
+
 def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, states: torch.Tensor,
-                   state_slots: torch.Tensor, cu_tokens: torch.Tensor, num_requests: int, heads: int, dim: int, value_dim: int) -> torch.Tensor:
+                   state_slots: torch.Tensor, cu_tokens: torch.Tensor, num_requests: int, heads: int, dim: int, value_dim: int,
+                   max_query_len: int = 0) -> torch.Tensor:
     """``S = decay[h] * S + k_t v_t^T``, ``o_t = S^T q_t`` per head over every request's new tokens
     ``cu_tokens[r]:cu_tokens[r+1]``, from and to ``states[state_slots[r]]`` (``[slots, heads, dim, value_dim]``
     float32).  ``q, k [N, heads * dim]`` float32, ``v [N, heads * value_dim]`` (a view with a row pitch will do).
-    Returns ``o [N, heads, value_dim]`` float32."""
+    Returns ``o [N, heads, value_dim]`` float32.  ``max_query_len``: the most tokens a request brings; long requests are
+    shared out over several CTAs in stretches (each walked from a zero state, the start states found by a short pass
+    over the stretches' end states, the missing term added in a third launch)."""
     _need(q.dtype == torch.float32 and k.dtype == torch.float32 and q.stride(1) == 1 and k.stride(1) == 1, "retention_scan: queries and keys are float32")
     _need(v.stride(1) == 1 and v.shape[1] == heads * value_dim, "retention_scan: v [N, heads * value_dim]")
     _need(states.dtype == torch.float32 and states.is_contiguous() and tuple(states.shape[1:]) == (heads, dim, value_dim), "retention_scan: states [slots, heads, dim, value_dim] float32")
@@ -1257,9 +1263,16 @@ def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: tor
     _i32(state_slots, "state_slots")
     _i32(cu_tokens, "cu_tokens")
     out = torch.empty((q.shape[0], heads, value_dim), dtype=torch.float32, device=q.device)
+    ctas = -(-value_dim // 16) * heads * int(num_requests)
+    stretches = max(1, min(8, int(max_query_len) // _RETENTION_MIN_STRETCH, -(-4 * _sm_count() // ctas), 65535 // max(1, int(num_requests))))
+    scratch = None
+    if stretches > 1:
+        scratch = torch.empty((2, int(num_requests) * stretches, heads, dim, value_dim), dtype=torch.float32, device=q.device)
     code = _launch("llm_retention_scan", _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), _code(v.dtype), v.stride(0), _ptr(decay),
-                   _ptr(states), _ptr(state_slots), _ptr(cu_tokens), _ptr(out), int(num_requests), heads, dim, value_dim, _stream())
+                   _ptr(states), _ptr(state_slots), _ptr(cu_tokens), _ptr(out), int(num_requests), heads, dim, value_dim, stretches,
+                   _ptr(scratch), _stream())
     _check(code, "retention_scan")
+    add_launches(2 * int(stretches > 1))
     return out
 
 

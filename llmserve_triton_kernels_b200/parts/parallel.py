@@ -6,6 +6,11 @@ each output RMS-normed over the model width by itself (``eps`` inside the root) 
 any registered mixer; what it keeps per request (pages, a state slot) is its own: the cache manager holds every
 branch's as a part of a ``CompositeSpec``.  The branches' products leave their results in 32-bit, the norms and the
 sum are 32-bit, and the result is a contribution to the residual stream.
+
+Branches that start with a stacked input product of their own (an attribute ``w_in`` and ``takes_projection = True``)
+hand their matrices over: the mixer stacks them once more, runs ONE product for all branches and gives each its
+columns of the result (``forward(..., proj=...)``).  The input may arrive in factored normalised form
+(``ops.NormedInput``) when every branch starts with a product that takes it.
 """
 
 from __future__ import annotations
@@ -29,6 +34,10 @@ class ParallelMixer(Mixer):
         for name, spec in branches.items():
             setattr(self, f"branch_{name}", build_part("mixer", spec))
         self.out_weights: list[torch.Tensor] = []
+        self.w_in: torch.Tensor | None = None  # the branches' input matrices stacked, where all of them hand theirs over
+        self._columns: list[tuple[int, int]] = []
+        # the stream in factored form is welcome if every branch's first step is a product that takes it
+        self.accepts_sink = all(getattr(b, "accepts_sink", False) for b in self.branches)
 
     @property
     def branches(self) -> list[Mixer]:
@@ -51,14 +60,27 @@ class ParallelMixer(Mixer):
         for name, branch in zip(self.branch_names, self.branches):
             branch.bind({local: tensors[f"{name}.{local}"] for local in branch.tensors()}, dtype, device)
             self.out_weights.append(tensors[f"{name}.{self.weight_name}"].to(device=device, dtype=torch.float32).contiguous())
+        if len(self.branches) > 1 and all(getattr(b, "takes_projection", False) and getattr(b, "w_in", None) is not None for b in self.branches):
+            self.w_in = torch.cat([b.w_in for b in self.branches], dim=0).contiguous()
+            start = 0
+            for b in self.branches:
+                self._columns.append((start, start + b.w_in.shape[0]))
+                start += b.w_in.shape[0]
+                b.w_in = None  # held here from now on: the branch is given its columns of the product
 
     def cache_spec(self) -> CompositeSpec:
         return CompositeSpec(tuple(b.cache_spec() for b in self.branches))
 
-    def forward(self, x, ctx, cache):
+    def forward(self, x, ctx, cache, sink=None):
+        """``sink`` is not used: what leaves this mixer is a sum of normed outputs, not a product."""
         outs = []
-        for branch, view in zip(self.branches, cache.parts):
-            out = branch.forward(x, ctx, view)
+        proj = ops.linear(x, self.w_in, out_dtype=torch.float32) if self.w_in is not None else None
+        for i, (branch, view) in enumerate(zip(self.branches, cache.parts)):
+            if proj is not None:
+                a, b = self._columns[i]
+                out = branch.forward(None, ctx, view, proj=proj[:, a:b])
+            else:
+                out = branch.forward(x, ctx, view)
             outs.append(out if out.dtype == torch.float32 else out.float())
         return ops.branch_norm_sum(outs, self.out_weights, self.norm_eps, self.factor)
 

@@ -78,6 +78,7 @@ class Retention(Mixer):
 
     graph_safe = True
     accepts_sink = True
+    takes_projection = True  # a mixer that runs this one beside others may run the input product itself (``forward(proj=)``)
 
     def __init__(self, hidden_size: int, num_heads: int, head_dim: int, value_dim: int, decay: list[float], norm_eps: float,
                  rotary: dict | None = None, gate: str = "silu", tensor_names: dict[str, str] | None = None):
@@ -113,12 +114,13 @@ class Retention(Mixer):
     def cache_spec(self) -> StateSpec:
         return StateSpec((self.num_heads, self.head_dim, self.value_dim), torch.float32)
 
-    def forward(self, x, ctx, cache, sink=None):
+    def forward(self, x, ctx, cache, sink=None, proj=None):
         H, D, V = self.num_heads, self.head_dim, self.value_dim
-        proj = ops.linear(x, self.w_in, out_dtype=torch.float32)  # [N, q | k | v | gate], 32-bit
+        if proj is None:
+            proj = ops.linear(x, self.w_in, out_dtype=torch.float32)  # [N, q | k | v | gate], 32-bit
         q, k = ops.qk_prepare(proj, ctx.positions, heads=H, kv_heads=H, dim=D, freq=self.freq, k_scale=D ** -0.5, out_dtype=torch.float32)
         o = ops.retention_scan(q, k, proj[:, 2 * H * D : 2 * H * D + H * V], self.decay, cache.states, cache.slots, ctx.cu_tokens,
-                               ctx.num_requests, H, D, V)
+                               ctx.num_requests, H, D, V, ctx.max_query_len)
         out = ops.head_norm_gate(o, proj[:, 2 * H * D + H * V :], self.norm_eps, self.gate, out_dtype=self.dtype)
         if sink is not None:
             handed_on = sink.linear(out, self.w_out)

@@ -46,6 +46,7 @@ def rotary_frequencies(dims: int, base: float, scaling: dict | None = None) -> t
 class SigmoidAttention(Mixer):
     graph_safe = True
     accepts_sink = True
+    takes_projection = True  # a mixer that runs this one beside others may run the input product itself (``forward(proj=)``)
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, scale: float,
                  softcap: float | None = None, rotary: dict | None = None, qk_norm_eps: float | None = None,
@@ -97,10 +98,12 @@ class SigmoidAttention(Mixer):
     def cache_spec(self) -> PagedKVSpec:
         return PagedKVSpec(self.num_kv_heads, max(self.head_dim, self.value_dim), self.window)
 
-    def forward(self, x, ctx, cache, sink=None):
+    def forward(self, x, ctx, cache, sink=None, proj=None):
+        """``proj``: the stacked projections ``[N, q | k | v]`` (32-bit, rows may have a pitch) where the caller ran the product."""
         H, KV, D, V = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim
         # the projections leave their product in 32-bit: the norm over the whole projection reads them as they are
-        proj = ops.linear(x, self.w_in, out_dtype=torch.float32)
+        if proj is None:
+            proj = ops.linear(x, self.w_in, out_dtype=torch.float32)
         q = ops.qk_prepare(proj, ctx.positions, heads=H, kv_heads=KV, dim=D, value_dim=V, freq=self.freq, q_weight=self.q_weight,
                            k_weight=self.k_weight, eps=self.qk_norm_eps or 0.0, pool=cache.pool, slot_map=cache.slot_map)
         out = ops.sigmoid_attention(q, cache.pool, cache.page_table, ctx, num_heads=H, num_kv_heads=KV, key_dim=D, value_dim=V,

@@ -353,7 +353,7 @@ def sigmoid_attention(q, pool, page_table, ctx, *, num_heads, num_kv_heads, key_
     return out
 
 
-def retention_scan(q, k, v, decay, states, state_slots, cu_tokens, num_requests, heads, dim, value_dim):
+def retention_scan(q, k, v, decay, states, state_slots, cu_tokens, num_requests, heads, dim, value_dim, max_query_len=0):
     n = q.shape[0]
     out = torch.empty((n, heads, value_dim), dtype=torch.float32, device=q.device)
     cu, slots = cu_tokens.tolist(), state_slots.tolist()

@@ -149,6 +149,13 @@ def test_retention_scan_and_head_norm(H, D, V, vdtype):
     o2 = plain_ops.retention_scan(q, k, v, decay, s2, slots, cu, 4, H, D, V)
     close(o1, o2, 1e-4, "outputs")
     close(s1, s2, 1e-4, "states")
+    # the same with the long request shared out over CTAs in stretches (the others are shorter than a stretch's turn of eight)
+    s3 = s1.clone().copy_(torch.randn(6, H, D, V, device=DEV))
+    s4 = s3.clone()
+    o3 = ops.retention_scan(q, k, v, decay, s3, slots, cu, 4, H, D, V, max_query_len=640)
+    o4 = plain_ops.retention_scan(q, k, v, decay, s4, slots, cu, 4, H, D, V)
+    close(o3, o4, 1e-4, "outputs, stretches")
+    close(s3, s4, 1e-4, "states, stretches")
     assert torch.equal(s1[[2, 4]], s2[[2, 4]])  # slots of no request are left alone
     gate = torch.randn(N, H * V + 3, device=DEV).to(vdtype)[:, : H * V]
     for kind in ("silu", "sigmoid"):
