@@ -3,16 +3,17 @@
 //   S_t = decay_h S_(t-1) + k_t v_t^T        o_t = S_t^T q_t            S: [D, V] float32, zero when a request starts
 //
 // Queries, keys, values, the state and the sums are 32-bit.  Column v of S is all that o_t[v] needs, so the columns
-// are shared out: a CTA owns 16 columns of one (request, head), eight threads a column, each with D / 8 rows of it in
-// registers.  The request's new tokens are walked in order and the slot is left with the state after the last.
+// are shared out: a CTA owns 64 (32, 16 for longer keys) columns of one (request, head) in 16 groups, eight threads a
+// group, each with D / 8 rows of the group's 4 (2, 1) columns in registers: what a thread reads of a token's q and k serves all
+// of its columns (with one column a thread the shared-memory reads, not the arithmetic, set the pace).  The request's new tokens are walked in order and the slot is left with the state after the last.
 //
 // Also here: the step behind it, each head's o divided by its root mean square and multiplied by a gate.
 #include "common.cuh"
 
 namespace {
 
-constexpr int COLS = 16;  // columns of the state a CTA owns
-constexpr int TPC = 8;    // threads a column
+constexpr int GROUPS = 16;  // groups of threads a CTA: each owns some neighbouring columns of the state
+constexpr int TPC = 8;      // threads a group: each holds D / 8 rows of the group's columns
 
 __device__ __forceinline__ void attn_cp16(float* smem, const float* gmem) {
     const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
@@ -38,23 +39,24 @@ __device__ __forceinline__ void stretch_of(int begin, int end, int s, int NS, in
     e = min(end, b + length);
 }
 
-template <typename TV, int DPT, int TB, bool CORRECT>
-__global__ void __launch_bounds__(COLS * TPC)
+template <typename TV, int DPT, int TB, int CPT, bool CORRECT>
+__global__ void __launch_bounds__(GROUPS * TPC)
 retention_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk, const TV* __restrict__ v, int ldv,
                       const float* __restrict__ decay, float* __restrict__ states, const int* __restrict__ state_slots,
                       const int* __restrict__ cu_tokens, float* __restrict__ out, int H, int D, int V, int NS,
                       float* __restrict__ ends, const float* __restrict__ starts) {
+    constexpr int COLS = GROUPS * CPT;  // columns of the state a CTA owns: 16 groups of threads, CPT neighbouring columns a thread
     constexpr int DS = DPT * TPC;   // rows of the state that the CTA's registers have room for (>= D)
     constexpr int SEG = DPT + 4;    // a part's lanes of a token's q or k, then 4 floats of room: the parts' 16-byte reads fall
     constexpr int RP = SEG * TPC;   // into different banks; RP: the pitch of a token's row
     extern __shared__ __align__(16) float shared[];
     float* tile = shared;                       // [DS][COLS + 1], the state on its way in and out
-    float* sq = tile + DS * (COLS + 1);         // [2][TB][RP]
+    float* sq = tile + DS * (COLS + 1) + (4 - (DS * (COLS + 1)) % 4) % 4;  // [2][TB][RP], on a 16-byte boundary
     float* sk = sq + 2 * TB * RP;               // [2][TB][RP]
     float* sv = sk + 2 * TB * RP;               // [2][TB][COLS]
     pdl_trigger();
     const int r = blockIdx.z / NS, stretch = blockIdx.z % NS, h = blockIdx.y, v0 = blockIdx.x * COLS;
-    const int sub = threadIdx.x % TPC, col = threadIdx.x / TPC;
+    const int sub = threadIdx.x % TPC, c0 = (threadIdx.x / TPC) * CPT;  // the thread's first column within the CTA's
     if (CORRECT && stretch == 0) return;  // the first stretch started from the true state
     int begin, end;
     stretch_of(cu_tokens[r], cu_tokens[r + 1], stretch, NS, begin, end);
@@ -90,7 +92,7 @@ retention_scan_kernel(const float* __restrict__ q, int ldq, const float* __restr
             }
         }
         if (CORRECT) {
-        } else if (vec_v) {  // the CTA's 16 lanes of a token's values: four copies of 16 bytes, in flight with the rest
+        } else if (vec_v) {  // the CTA's lanes of a token's values in copies of 16 bytes, in flight with the rest
             for (int i = threadIdx.x; i < count * (COLS / 4); i += blockDim.x) {
                 const int tt = i / (COLS / 4), c = (i % (COLS / 4)) * 4;
                 attn_cp16(sv + ((size_t)buf * TB + tt) * COLS + c, reinterpret_cast<const float*>(v) + (size_t)(t0 + tt) * ldv + (size_t)h * V + v0 + c);
@@ -117,13 +119,59 @@ retention_scan_kernel(const float* __restrict__ q, int ldq, const float* __restr
         tile[d * (COLS + 1) + c] = (state_in && v0 + c < V) ? state_in[(size_t)d * V + v0 + c] : 0.f;
     }
     __syncthreads();
-    float S[DPT];
+    float S[CPT][DPT];
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) {
-        const int d = sub * DPT + i;
-        S[i] = d < D ? tile[d * (COLS + 1) + col] : 0.f;
-    }
-    const bool live = v0 + col < V;
+    for (int c = 0; c < CPT; ++c)
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            const int d = sub * DPT + i;
+            S[c][i] = d < D ? tile[d * (COLS + 1) + c0 + c] : 0.f;
+        }
+    // the thread's columns that exist, and whether its outputs of a token may be stored 16 bytes at a time
+    const int live = max(0, min(CPT, V - (v0 + c0)));
+    const bool wide_out = CPT == 4 && live == 4 && V % 4 == 0;
+    // one token: the state moves on (not when CORRECT) and acc[c] takes this thread's share of o_t[column c]
+    auto token = [&](const float* bq, const float* bk, const float* bv, float (&acc)[CPT]) {
+        float vt[CPT];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+            vt[c] = CORRECT ? 0.f : bv[c];
+            acc[c] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < DPT; i += 4) {
+            const float4 q4 = *reinterpret_cast<const float4*>(bq + i);
+            const float qv[4] = {q4.x, q4.y, q4.z, q4.w};
+            float kv[4] = {0.f, 0.f, 0.f, 0.f};
+            if (!CORRECT) {
+                const float4 k4 = *reinterpret_cast<const float4*>(bk + i);
+                kv[0] = k4.x; kv[1] = k4.y; kv[2] = k4.z; kv[3] = k4.w;
+            }
+#pragma unroll
+            for (int c = 0; c < CPT; ++c)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (!CORRECT) S[c][i + j] = fmaf(gamma, S[c][i + j], kv[j] * vt[c]);
+                    acc[c] = fmaf(S[c][i + j], qv[j], acc[c]);
+                }
+        }
+    };
+    auto store = [&](int t, const float (&total)[CPT]) {
+        float* at = out + ((size_t)t * H + h) * V + v0 + c0;
+        const float f = CORRECT ? exp2f((float)(t - begin + 1) * log2_gamma) : 0.f;
+        if (wide_out) {
+            float4 o = make_float4(total[0], total[1], total[2], total[3]);
+            if (CORRECT) {
+                const float4 b4 = *reinterpret_cast<const float4*>(at);
+                o = make_float4(fmaf(o.x, f, b4.x), fmaf(o.y, f, b4.y), fmaf(o.z, f, b4.z), fmaf(o.w, f, b4.w));
+            }
+            *reinterpret_cast<float4*>(at) = o;
+        } else {
+#pragma unroll
+            for (int c = 0; c < CPT; ++c)
+                if (c < live) at[c] = CORRECT ? fmaf(total[c], f, at[c]) : total[c];
+        }
+    };
     int buf = 0;
     for (int t0 = begin; t0 < end; t0 += TB, buf ^= 1) {
         asm volatile("cp.async.wait_group 0;\n" ::);
@@ -132,80 +180,49 @@ retention_scan_kernel(const float* __restrict__ q, int ldq, const float* __restr
         const int count = min(TB, end - t0);
         const float* bq = sq + (size_t)buf * TB * RP + sub * SEG;
         const float* bk = sk + (size_t)buf * TB * RP + sub * SEG;
-        const float* bv = sv + (size_t)buf * TB * COLS + col;
+        const float* bv = sv + (size_t)buf * TB * COLS + c0;
         int tt = 0;
         // eight tokens at a time: their partial sums are independent chains, and the eight lanes of a column then
-        // trade halves (4, 2, 1 values) so that lane `sub` ends with the whole sum of token tt + sub: 7 shuffles for
-        // 8 tokens, and every lane stores one value
+        // trade halves (4, 2, 1 values) so that lane `sub` ends with the whole sums of token tt + sub: 7 shuffles a
+        // column for 8 tokens, and every lane stores one token's columns
         for (; tt + 8 <= count; tt += 8) {
-            float* mine = out + ((size_t)(t0 + tt + sub) * H + h) * V + v0 + col;  // lane `sub` ends with token tt + sub
-            const float before = (CORRECT && live) ? *mine : 0.f;                   // asked for now, wanted at the turn's end
-            float o[8];
+            float o[8][CPT];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const float vt = CORRECT ? 0.f : bv[(tt + u) * COLS];
-                float acc = 0.f;
-#pragma unroll
-                for (int i = 0; i < DPT; i += 4) {
-                    const float4 q4 = *reinterpret_cast<const float4*>(bq + (size_t)(tt + u) * RP + i);
-                    if (!CORRECT) {
-                        const float4 k4 = *reinterpret_cast<const float4*>(bk + (size_t)(tt + u) * RP + i);
-                        S[i] = fmaf(gamma, S[i], k4.x * vt);
-                        S[i + 1] = fmaf(gamma, S[i + 1], k4.y * vt);
-                        S[i + 2] = fmaf(gamma, S[i + 2], k4.z * vt);
-                        S[i + 3] = fmaf(gamma, S[i + 3], k4.w * vt);
-                    }
-                    acc = fmaf(S[i], q4.x, acc);
-                    acc = fmaf(S[i + 1], q4.y, acc);
-                    acc = fmaf(S[i + 2], q4.z, acc);
-                    acc = fmaf(S[i + 3], q4.w, acc);
-                }
-                o[u] = acc;
-            }
+            for (int u = 0; u < 8; ++u) token(bq + (size_t)(tt + u) * RP, bk + (size_t)(tt + u) * RP, bv + (size_t)(tt + u) * COLS, o[u]);
             const bool h4 = sub & 4, h2 = sub & 2, h1 = sub & 1;
-            float a[4], b[2];
+            float total[CPT];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) a[u] = (h4 ? o[u + 4] : o[u]) + __shfl_xor_sync(0xffffffffu, h4 ? o[u] : o[u + 4], 4);
+            for (int c = 0; c < CPT; ++c) {
+                float a[4], b[2];
 #pragma unroll
-            for (int u = 0; u < 2; ++u) b[u] = (h2 ? a[u + 2] : a[u]) + __shfl_xor_sync(0xffffffffu, h2 ? a[u] : a[u + 2], 2);
-            const float total = (h1 ? b[1] : b[0]) + __shfl_xor_sync(0xffffffffu, h1 ? b[0] : b[1], 1);
-            if (live) *mine = CORRECT ? fmaf(total, exp2f((float)(t0 + tt + sub - begin + 1) * log2_gamma), before) : total;
+                for (int u = 0; u < 4; ++u) a[u] = (h4 ? o[u + 4][c] : o[u][c]) + __shfl_xor_sync(0xffffffffu, h4 ? o[u][c] : o[u + 4][c], 4);
+#pragma unroll
+                for (int u = 0; u < 2; ++u) b[u] = (h2 ? a[u + 2] : a[u]) + __shfl_xor_sync(0xffffffffu, h2 ? a[u] : a[u + 2], 2);
+                total[c] = (h1 ? b[1] : b[0]) + __shfl_xor_sync(0xffffffffu, h1 ? b[0] : b[1], 1);
+            }
+            store(t0 + tt + sub, total);
         }
         for (; tt < count; ++tt) {
-            const float vt = CORRECT ? 0.f : bv[tt * COLS];
-            float o = 0.f;
+            float acc[CPT];
+            token(bq + (size_t)tt * RP, bk + (size_t)tt * RP, bv + (size_t)tt * COLS, acc);
 #pragma unroll
-            for (int i = 0; i < DPT; i += 4) {
-                const float4 q4 = *reinterpret_cast<const float4*>(bq + (size_t)tt * RP + i);
-                if (!CORRECT) {
-                    const float4 k4 = *reinterpret_cast<const float4*>(bk + (size_t)tt * RP + i);
-                    S[i] = fmaf(gamma, S[i], k4.x * vt);
-                    S[i + 1] = fmaf(gamma, S[i + 1], k4.y * vt);
-                    S[i + 2] = fmaf(gamma, S[i + 2], k4.z * vt);
-                    S[i + 3] = fmaf(gamma, S[i + 3], k4.w * vt);
-                }
-                o = fmaf(S[i], q4.x, o);
-                o = fmaf(S[i + 1], q4.y, o);
-                o = fmaf(S[i + 2], q4.z, o);
-                o = fmaf(S[i + 3], q4.w, o);
+            for (int c = 0; c < CPT; ++c) {
+                acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 1);
+                acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 2);
+                acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 4);
             }
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            o += __shfl_xor_sync(0xffffffffu, o, 4);
-            if (sub == 0 && live) {
-                float* at = out + ((size_t)(t0 + tt) * H + h) * V + v0 + col;
-                if (CORRECT) *at += o * exp2f((float)(t0 + tt - begin + 1) * log2_gamma);
-                else *at = o;
-            }
+            if (sub == 0) store(t0 + tt, acc);
         }
     }
     if (CORRECT) return;
     __syncthreads();
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) {
-        const int d = sub * DPT + i;
-        if (d < D) tile[d * (COLS + 1) + col] = S[i];
-    }
+    for (int c = 0; c < CPT; ++c)
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            const int d = sub * DPT + i;
+            if (d < D) tile[d * (COLS + 1) + c0 + c] = S[c][i];
+        }
     __syncthreads();
     for (int i = threadIdx.x; i < D * COLS; i += blockDim.x) {
         const int d = i / COLS, c = i % COLS;
@@ -272,13 +289,14 @@ LLM_EXPORT int llm_retention_scan(const float* q, int ldq, const float* k, int l
     if (H <= 0 || D <= 0 || V <= 0 || D > 256 || H > 65535 || stretches < 1 || (stretches > 1 && !scratch) || (long long)requests * stretches > 65535)
         return LLM_ERR_BAD_ARGUMENT;
     const int NS = stretches;
-    const dim3 grid((V + COLS - 1) / COLS, H, requests * NS), block(COLS * TPC);
+    const int cpt = D <= 64 ? 4 : D <= 128 ? 2 : 1, cols = GROUPS * cpt;
+    const dim3 grid((V + cols - 1) / cols, H, requests * NS), block(GROUPS * TPC);
     float* ends = scratch;
     float* starts = scratch ? scratch + (size_t)requests * NS * H * D * V : nullptr;
     using bf = __nv_bfloat16;
     auto go = [&](auto kernel, auto* vp, int dpt, int tb) -> int {
         const int ds = dpt * TPC;
-        const size_t smem = ((size_t)ds * (COLS + 1) + (size_t)4 * tb * (dpt + 4) * TPC + (size_t)2 * tb * COLS) * sizeof(float);
+        const size_t smem = ((size_t)ds * (cols + 1) + 4 + (size_t)4 * tb * (dpt + 4) * TPC + (size_t)2 * tb * cols) * sizeof(float);
         if (smem > 48 * 1024) {
             const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
@@ -286,9 +304,9 @@ LLM_EXPORT int llm_retention_scan(const float* q, int ldq, const float* k, int l
         return launch_pdl(kernel, grid, block, smem, stream, q, ldq, k, ldk, vp, ldv, decay, states, state_slots, cu_tokens, out, H, D, V, NS, ends,
                           (const float*)starts);
     };
-#define LLM_RET2(DPT, TB, C) \
-    (v_dtype == LLM_F32 ? go(retention_scan_kernel<float, DPT, TB, C>, (const float*)v, DPT, TB) : go(retention_scan_kernel<bf, DPT, TB, C>, (const bf*)v, DPT, TB))
-#define LLM_RET(C) (D <= 32 ? LLM_RET2(4, 32, C) : D <= 64 ? LLM_RET2(8, 32, C) : D <= 128 ? LLM_RET2(16, 16, C) : LLM_RET2(32, 8, C))
+#define LLM_RET2(DPT, TB, CPT, C) \
+    (v_dtype == LLM_F32 ? go(retention_scan_kernel<float, DPT, TB, CPT, C>, (const float*)v, DPT, TB) : go(retention_scan_kernel<bf, DPT, TB, CPT, C>, (const bf*)v, DPT, TB))
+#define LLM_RET(C) (D <= 32 ? LLM_RET2(4, 32, 4, C) : D <= 64 ? LLM_RET2(8, 32, 4, C) : D <= 128 ? LLM_RET2(16, 16, 2, C) : LLM_RET2(32, 8, 1, C))
     int code = LLM_RET(false);
     if (code != 0 || NS == 1) return code;
     const int per_head = D * V;

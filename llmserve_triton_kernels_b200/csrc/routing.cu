@@ -100,15 +100,15 @@ router_kernel(const TX* __restrict__ x, int ldx, const float* __restrict__ wr, c
 #pragma unroll 4
             for (int k = lane * 4; k < K; k += 128) {
                 const float4 wv = *reinterpret_cast<const float4*>(w + k);
+                float xv[TT][4];  // every load of the turn asked for before the first sum (rows beyond the last token read the last one's)
+#pragma unroll
+                for (int tt = 0; tt < TT; ++tt) load4(x + (size_t)min(t0 + tt, N - 1) * ldx + k, xv[tt]);
 #pragma unroll
                 for (int tt = 0; tt < TT; ++tt) {
-                    if (t0 + tt >= N) continue;
-                    float xv[4];
-                    load4(x + (size_t)(t0 + tt) * ldx + k, xv);
-                    acc[tt] = fmaf(wv.x, xv[0], acc[tt]);
-                    acc[tt] = fmaf(wv.y, xv[1], acc[tt]);
-                    acc[tt] = fmaf(wv.z, xv[2], acc[tt]);
-                    acc[tt] = fmaf(wv.w, xv[3], acc[tt]);
+                    acc[tt] = fmaf(wv.x, xv[tt][0], acc[tt]);
+                    acc[tt] = fmaf(wv.y, xv[tt][1], acc[tt]);
+                    acc[tt] = fmaf(wv.z, xv[tt][2], acc[tt]);
+                    acc[tt] = fmaf(wv.w, xv[tt][3], acc[tt]);
                 }
             }
         } else {
@@ -116,8 +116,7 @@ router_kernel(const TX* __restrict__ x, int ldx, const float* __restrict__ wr, c
             for (int k = lane; k < K; k += 32) {
                 const float wv = w[k];
 #pragma unroll
-                for (int tt = 0; tt < TT; ++tt)
-                    if (t0 + tt < N) acc[tt] = fmaf(wv, to_float(x[(size_t)(t0 + tt) * ldx + k]), acc[tt]);
+                for (int tt = 0; tt < TT; ++tt) acc[tt] = fmaf(wv, to_float(x[(size_t)min(t0 + tt, N - 1) * ldx + k]), acc[tt]);
             }
         }
 #pragma unroll

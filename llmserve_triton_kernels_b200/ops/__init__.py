@@ -1263,7 +1263,8 @@ def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: tor
     _i32(state_slots, "state_slots")
     _i32(cu_tokens, "cu_tokens")
     out = torch.empty((q.shape[0], heads, value_dim), dtype=torch.float32, device=q.device)
-    ctas = -(-value_dim // 16) * heads * int(num_requests)
+    cols = 64 if dim <= 64 else 32 if dim <= 128 else 16  # columns of the state that one CTA owns (csrc/retention.cu)
+    ctas = -(-value_dim // cols) * heads * int(num_requests)
     stretches = max(1, min(8, int(max_query_len) // _RETENTION_MIN_STRETCH, -(-4 * _sm_count() // ctas), 65535 // max(1, int(num_requests))))
     scratch = None
     if stretches > 1:
