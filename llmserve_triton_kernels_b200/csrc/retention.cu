@@ -281,15 +281,16 @@ head_norm_gate_kernel(const float* __restrict__ o, const TG* __restrict__ g, int
 
 }  // namespace
 
-// `stretches` > 1: long requests shared out over that many CTAs each; `scratch` then holds 2 * requests * stretches * H * D * V floats.
+// `few_tokens`: no request brings more than a few tokens.  `stretches` > 1: long requests shared out over that many CTAs each; `scratch` then holds 2 * requests * stretches * H * D * V floats.
 LLM_EXPORT int llm_retention_scan(const float* q, int ldq, const float* k, int ldk, const void* v, int v_dtype, int ldv,
                                   const float* decay, float* states, const int* state_slots, const int* cu_tokens, float* out,
-                                  int requests, int H, int D, int V, int stretches, float* scratch, cudaStream_t stream) {
+                                  int requests, int H, int D, int V, int stretches, float* scratch, int few_tokens, cudaStream_t stream) {
     if (requests <= 0) return 0;
     if (H <= 0 || D <= 0 || V <= 0 || D > 256 || H > 65535 || stretches < 1 || (stretches > 1 && !scratch) || (long long)requests * stretches > 65535)
         return LLM_ERR_BAD_ARGUMENT;
     const int NS = stretches;
-    const int cpt = D <= 64 ? 4 : D <= 128 ? 2 : 1, cols = GROUPS * cpt;
+    // steps of few tokens a request (decode steps) move the state more than they compute: 16 columns a CTA, more CTAs
+    const int cpt = few_tokens ? 1 : D <= 64 ? 4 : D <= 128 ? 2 : 1, cols = GROUPS * cpt;
     const dim3 grid((V + cols - 1) / cols, H, requests * NS), block(GROUPS * TPC);
     float* ends = scratch;
     float* starts = scratch ? scratch + (size_t)requests * NS * H * D * V : nullptr;
@@ -306,7 +307,9 @@ LLM_EXPORT int llm_retention_scan(const float* q, int ldq, const float* k, int l
     };
 #define LLM_RET2(DPT, TB, CPT, C) \
     (v_dtype == LLM_F32 ? go(retention_scan_kernel<float, DPT, TB, CPT, C>, (const float*)v, DPT, TB) : go(retention_scan_kernel<bf, DPT, TB, CPT, C>, (const bf*)v, DPT, TB))
-#define LLM_RET(C) (D <= 32 ? LLM_RET2(4, 32, 4, C) : D <= 64 ? LLM_RET2(8, 32, 4, C) : D <= 128 ? LLM_RET2(16, 16, 2, C) : LLM_RET2(32, 8, 1, C))
+#define LLM_RET(C)                                                                                                              \
+    (few_tokens ? (D <= 32 ? LLM_RET2(4, 32, 1, C) : D <= 64 ? LLM_RET2(8, 32, 1, C) : D <= 128 ? LLM_RET2(16, 16, 1, C) : LLM_RET2(32, 8, 1, C)) \
+                : (D <= 32 ? LLM_RET2(4, 32, 4, C) : D <= 64 ? LLM_RET2(8, 32, 4, C) : D <= 128 ? LLM_RET2(16, 16, 2, C) : LLM_RET2(32, 8, 1, C)))
     int code = LLM_RET(false);
     if (code != 0 || NS == 1) return code;
     const int per_head = D * V;

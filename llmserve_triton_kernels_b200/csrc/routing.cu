@@ -75,55 +75,74 @@ route_topk_kernel(const float* __restrict__ z, int ldz, const float* __restrict_
 }
 
 // The router's product and the choice in one kernel.  x: [N, K] (any type, read as 32-bit); wr: [E (+ 1), K] float32 (the last
-// row, if there is a shared gate, is the gate's); a CTA takes TT tokens: warp w sums up the logits of rows w, w + warps, ... for all of
+// row, if there is a shared gate, is the gate's); a CTA takes TT tokens (1 or 2): a warp sums up the logits of four rows at a time for all of
 // them (a lane its share of the elements, then the lanes' sums: the same order whatever else is in the step), then a warp per token
 // chooses.
 template <typename TX, int TT>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(512)
 router_kernel(const TX* __restrict__ x, int ldx, const float* __restrict__ wr, const float* __restrict__ correction, float* __restrict__ out,
               int N, int K, int E, int top, float scale, int renorm, int shared_gate) {
+    constexpr int RPW = 4;  // rows of the router matrix a warp sums up at once: what it reads of the tokens serves all four
     extern __shared__ float sm[];  // z[TT][rows], then per token s[E], c[E]
     pdl_trigger();
     const int rows = E + shared_gate, t0 = blockIdx.x * TT;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     float* z = sm;
     pdl_wait();
-    const int warps = blockDim.x >> 5;
     // four elements a lane and turn where rows allow 16-byte (weights) and 4-element (x) loads; the lanes' order of sums is fixed
     const bool wide = K % 4 == 0 && ldx % 4 == 0 && reinterpret_cast<uintptr_t>(wr) % 16 == 0 && reinterpret_cast<uintptr_t>(x) % (4 * sizeof(TX)) == 0;
-    for (int e = warp; e < rows; e += warps) {
-        float acc[TT];
+    for (int e0 = warp * RPW; e0 < rows; e0 += warps * RPW) {
+        float acc[RPW][TT];
 #pragma unroll
-        for (int tt = 0; tt < TT; ++tt) acc[tt] = 0.f;
-        const float* w = wr + (size_t)e * K;
+        for (int r = 0; r < RPW; ++r)
+#pragma unroll
+            for (int tt = 0; tt < TT; ++tt) acc[r][tt] = 0.f;
+        const float* w[RPW];
+        const TX* xr[TT];
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) w[r] = wr + (size_t)min(e0 + r, rows - 1) * K;  // rows beyond the last read the last one's; not stored
+#pragma unroll
+        for (int tt = 0; tt < TT; ++tt) xr[tt] = x + (size_t)min(t0 + tt, N - 1) * ldx;
         if (wide) {
-#pragma unroll 4
+#pragma unroll(TT == 1 ? 4 : 2)
             for (int k = lane * 4; k < K; k += 128) {
-                const float4 wv = *reinterpret_cast<const float4*>(w + k);
-                float xv[TT][4];  // every load of the turn asked for before the first sum (rows beyond the last token read the last one's)
+                float4 wv[RPW];
+                float xv[TT][4];
 #pragma unroll
-                for (int tt = 0; tt < TT; ++tt) load4(x + (size_t)min(t0 + tt, N - 1) * ldx + k, xv[tt]);
+                for (int r = 0; r < RPW; ++r) wv[r] = *reinterpret_cast<const float4*>(w[r] + k);
 #pragma unroll
-                for (int tt = 0; tt < TT; ++tt) {
-                    acc[tt] = fmaf(wv.x, xv[tt][0], acc[tt]);
-                    acc[tt] = fmaf(wv.y, xv[tt][1], acc[tt]);
-                    acc[tt] = fmaf(wv.z, xv[tt][2], acc[tt]);
-                    acc[tt] = fmaf(wv.w, xv[tt][3], acc[tt]);
-                }
+                for (int tt = 0; tt < TT; ++tt) load4(xr[tt] + k, xv[tt]);
+#pragma unroll
+                for (int r = 0; r < RPW; ++r)
+#pragma unroll
+                    for (int tt = 0; tt < TT; ++tt) {
+                        acc[r][tt] = fmaf(wv[r].x, xv[tt][0], acc[r][tt]);
+                        acc[r][tt] = fmaf(wv[r].y, xv[tt][1], acc[r][tt]);
+                        acc[r][tt] = fmaf(wv[r].z, xv[tt][2], acc[r][tt]);
+                        acc[r][tt] = fmaf(wv[r].w, xv[tt][3], acc[r][tt]);
+                    }
             }
         } else {
-#pragma unroll 4
+#pragma unroll 2
             for (int k = lane; k < K; k += 32) {
-                const float wv = w[k];
+                float wv[RPW], xv[TT];
 #pragma unroll
-                for (int tt = 0; tt < TT; ++tt) acc[tt] = fmaf(wv, to_float(x[(size_t)min(t0 + tt, N - 1) * ldx + k]), acc[tt]);
+                for (int r = 0; r < RPW; ++r) wv[r] = w[r][k];
+#pragma unroll
+                for (int tt = 0; tt < TT; ++tt) xv[tt] = to_float(xr[tt][k]);
+#pragma unroll
+                for (int r = 0; r < RPW; ++r)
+#pragma unroll
+                    for (int tt = 0; tt < TT; ++tt) acc[r][tt] = fmaf(wv[r], xv[tt], acc[r][tt]);
             }
         }
 #pragma unroll
-        for (int tt = 0; tt < TT; ++tt) {
-            const float v = warp_sum(acc[tt]);
-            if (lane == 0) z[tt * rows + e] = v;
-        }
+        for (int r = 0; r < RPW; ++r)
+#pragma unroll
+            for (int tt = 0; tt < TT; ++tt) {
+                const float v = warp_sum(acc[r][tt]);
+                if (lane == 0 && e0 + r < rows) z[tt * rows + e0 + r] = v;
+            }
     }
     __syncthreads();
     if (warp < TT && t0 + warp < N) {
@@ -234,21 +253,22 @@ LLM_EXPORT int llm_router(const void* x, int x_dtype, int ldx, const float* wr, 
                           int top, float scale, int renorm, int shared_gate, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (E <= 0 || top < 1 || top > E || E > 2048 || K <= 0) return LLM_ERR_BAD_ARGUMENT;
-    constexpr int TT = 4;
-    const int rows = E + (shared_gate ? 1 : 0);
-    const size_t smem = ((size_t)TT * rows + (size_t)TT * 2 * E) * sizeof(float);
+    // tokens a CTA: one for steps of few tokens (more CTAs, more loads in flight a warp), two otherwise (three CTAs an SM)
+    const int TT = N <= 32 ? 1 : 2;
     const int rows_all = E + (shared_gate ? 1 : 0);
-    const int warps = rows_all < 8 ? 8 : rows_all > 32 ? 32 : rows_all;  // a warp a row of the router where they fit
-    const dim3 grid((N + TT - 1) / TT), block(32 * warps);
-    if (smem > 48 * 1024) {
-        const cudaError_t e = x_dtype == LLM_F32 ? cudaFuncSetAttribute(router_kernel<float, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                                                 : cudaFuncSetAttribute(router_kernel<__nv_bfloat16, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-    }
-    if (x_dtype == LLM_F32)
-        return launch_pdl(router_kernel<float, TT>, grid, block, smem, stream, (const float*)x, ldx, wr, correction, out, N, K, E, top, scale, renorm, shared_gate ? 1 : 0);
-    return launch_pdl(router_kernel<__nv_bfloat16, TT>, grid, block, smem, stream, (const __nv_bfloat16*)x, ldx, wr, correction, out, N, K, E, top, scale,
-                      renorm, shared_gate ? 1 : 0);
+    const size_t smem = ((size_t)TT * rows_all + (size_t)TT * 2 * E) * sizeof(float);
+    const int groups = (rows_all + 3) / 4;  // of four rows: a warp each, as far as 16 warps go
+    const dim3 grid((N + TT - 1) / TT), block(32 * (groups < 4 ? 4 : groups > 16 ? 16 : groups));
+    auto go = [&](auto kernel, auto* xp) -> int {
+        if (smem > 48 * 1024) {
+            const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        return launch_pdl(kernel, grid, block, smem, stream, xp, ldx, wr, correction, out, N, K, E, top, scale, renorm, shared_gate ? 1 : 0);
+    };
+    using bf = __nv_bfloat16;
+    if (x_dtype == LLM_F32) return TT == 1 ? go(router_kernel<float, 1>, (const float*)x) : go(router_kernel<float, 2>, (const float*)x);
+    return TT == 1 ? go(router_kernel<bf, 1>, (const bf*)x) : go(router_kernel<bf, 2>, (const bf*)x);
 }
 
 LLM_EXPORT int llm_expert_act_scale(const void* x, int ldx, const float* w, int ldw, void* y, int ldy, int dtype, int N, int C, int E,

@@ -62,7 +62,7 @@ _SIGNATURES = {
     "llm_sigmoid_attention_mma": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i, _i, _vp],
     "llm_sigmoid_sum_parts": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
     "llm_qk_prepare": [_vp, _i, _i, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _f, _vp, _i, _vp, _f, _i, _i, _i, _i, _i, _vp],
-    "llm_retention_scan": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
+    "llm_retention_scan": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp],
     "llm_head_norm_gate": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _i, _vp],
     "llm_router": [_vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
     "llm_route_topk": [_vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp],
@@ -1263,7 +1263,8 @@ def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: tor
     _i32(state_slots, "state_slots")
     _i32(cu_tokens, "cu_tokens")
     out = torch.empty((q.shape[0], heads, value_dim), dtype=torch.float32, device=q.device)
-    cols = 64 if dim <= 64 else 32 if dim <= 128 else 16  # columns of the state that one CTA owns (csrc/retention.cu)
+    few = 0 < int(max_query_len) <= 16  # a decode step, or portions of a few tokens
+    cols = 16 if few else 64 if dim <= 64 else 32 if dim <= 128 else 16  # columns of the state that one CTA owns (csrc/retention.cu)
     ctas = -(-value_dim // cols) * heads * int(num_requests)
     stretches = max(1, min(8, int(max_query_len) // _RETENTION_MIN_STRETCH, -(-4 * _sm_count() // ctas), 65535 // max(1, int(num_requests))))
     scratch = None
@@ -1271,7 +1272,7 @@ def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: tor
         scratch = torch.empty((2, int(num_requests) * stretches, heads, dim, value_dim), dtype=torch.float32, device=q.device)
     code = _launch("llm_retention_scan", _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), _code(v.dtype), v.stride(0), _ptr(decay),
                    _ptr(states), _ptr(state_slots), _ptr(cu_tokens), _ptr(out), int(num_requests), heads, dim, value_dim, stretches,
-                   _ptr(scratch), _stream())
+                   _ptr(scratch), int(few), _stream())
     _check(code, "retention_scan")
     add_launches(2 * int(stretches > 1))
     return out

@@ -149,6 +149,11 @@ def test_retention_scan_and_head_norm(H, D, V, vdtype):
     o2 = plain_ops.retention_scan(q, k, v, decay, s2, slots, cu, 4, H, D, V)
     close(o1, o2, 1e-4, "outputs")
     close(s1, s2, 1e-4, "states")
+    s5, s6 = s1.clone(), s2.clone()  # the form for steps of few tokens a request (16 columns a CTA)
+    few_cu = torch.tensor([0, 3, 4, 9, 11], dtype=torch.int32, device=DEV)
+    close(ops.retention_scan(q[:11], k[:11], v[:11], decay, s5, slots, few_cu, 4, H, D, V, max_query_len=5),
+          plain_ops.retention_scan(q[:11], k[:11], v[:11], decay, s6, slots, few_cu, 4, H, D, V), 1e-4, "outputs, few tokens")
+    close(s5, s6, 1e-4, "states, few tokens")
     # the same with the long request shared out over CTAs in stretches (the others are shorter than a stretch's turn of eight)
     s3 = s1.clone().copy_(torch.randn(6, H, D, V, device=DEV))
     s4 = s3.clone()
