@@ -234,7 +234,70 @@ branch_norm_sum_kernel(Branches br, int count, float* __restrict__ out, int C, f
     }
 }
 
+// The same, straight into the residual stream and through the norm behind it:
+//   resid[t, :] += factor * sum_b rmsnorm(x_b[t, :]) * w_b;   out[t, :] = resid[t, :] / sqrt(mean(resid[t, :]^2) + eps_n) * wn
+// One CTA a row; the branches' rows and the stream's new row wait in shared memory between the passes.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+branch_sum_norm_kernel(Branches br, int count, float* __restrict__ resid, const float* __restrict__ wn, TO* __restrict__ out, int C, float eps,
+                       float factor, float eps_n) {
+    extern __shared__ float rowbuf[];  // [count + 1][C]
+    __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
+    const size_t row = (size_t)blockIdx.x * C;
+    float scale[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        if (b >= count) break;
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < C; i += blockDim.x) {
+            const float v = br.x[b][row + i];
+            rowbuf[b * C + i] = v;
+            ss = fmaf(v, v, ss);
+        }
+        ss = block_sum(ss, scratch);
+        scale[b] = 1.f / sqrtf(ss / (float)C + eps);
+    }
+    float* fresh = rowbuf + (size_t)count * C;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < C; i += blockDim.x) {
+        float s = 0.f;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            if (b >= count) break;
+            s += rowbuf[b * C + i] * scale[b] * br.w[b][i];
+        }
+        const float v = resid[row + i] + s * factor;
+        resid[row + i] = v;
+        fresh[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float sn = 1.f / sqrtf(ss / (float)C + eps_n);
+    for (int i = threadIdx.x; i < C; i += blockDim.x) out[row + i] = from_float<TO>(fresh[i] * sn * wn[i]);
+}
+
 }  // namespace
+
+LLM_EXPORT int llm_branch_sum_norm(const float* x0, const float* w0, const float* x1, const float* w1, const float* x2, const float* w2,
+                                   const float* x3, const float* w3, int count, float* resid, const float* wn, void* out, int out_dtype, int N,
+                                   int C, float eps, float factor, float eps_n, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (count < 1 || count > 4 || C <= 0) return LLM_ERR_BAD_ARGUMENT;
+    const size_t need = (size_t)(count + 1) * C * sizeof(float);
+    if (need > 160 * 1024) return LLM_ERR_UNSUPPORTED;
+    Branches br = {{x0, x1, x2, x3}, {w0, w1, w2, w3}};
+    auto go = [&](auto kernel, auto* op) -> int {
+        if (need > 48 * 1024) {
+            const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need);
+            if (e != cudaSuccess) return (int)e;
+        }
+        return launch_pdl(kernel, dim3(N), dim3(256), need, stream, br, count, resid, wn, op, C, eps, factor, eps_n);
+    };
+    if (out_dtype == LLM_F32) return go(branch_sum_norm_kernel<float>, (float*)out);
+    return go(branch_sum_norm_kernel<__nv_bfloat16>, (__nv_bfloat16*)out);
+}
 
 LLM_EXPORT int llm_route_topk(const float* z, int ldz, const float* correction, float* w, int N, int E, int top, float scale,
                               int renorm, int shared_gate, cudaStream_t stream) {

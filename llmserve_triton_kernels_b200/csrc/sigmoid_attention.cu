@@ -162,7 +162,7 @@ qk_prepare_kernel(const TI* __restrict__ proj, int ldp, TQ* __restrict__ q_out, 
     pdl_trigger();
     const int t = blockIdx.x;
     const int half = rot >> 1;
-    const float position = (float)positions[t];
+    const float position = half > 0 ? (float)positions[t] : 0.f;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         float s, c;
         sincosf(position * freq[i], &s, &c);

@@ -67,6 +67,7 @@ _SIGNATURES = {
     "llm_router": [_vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
     "llm_route_topk": [_vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp],
     "llm_expert_act_scale": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "llm_branch_sum_norm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _f, _f, _f, _vp],
     "llm_branch_norm_sum": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _f, _f, _vp],
 }
 
@@ -336,8 +337,22 @@ class Scaled:
         self.tensor, self.alpha = tensor, float(alpha)
 
 
+class BranchSum:
+    """A contribution that is still a list of branch outputs: ``factor * sum_b rmsnorm(branches[b]) * weights[b]`` (what
+    mixers side by side return).  A norm that knows it (``add_branches``) adds it to the stream and normalises in one
+    kernel (:func:`branch_sum_rmsnorm`); anybody else gets the tensor from :meth:`materialize`."""
+
+    def __init__(self, branches: list[torch.Tensor], weights: list[torch.Tensor], eps: float, factor: float):
+        self.branches, self.weights, self.eps, self.factor = branches, weights, float(eps), float(factor)
+
+    def materialize(self) -> torch.Tensor:
+        return branch_norm_sum(self.branches, self.weights, self.eps, self.factor)
+
+
 def split_pending(pending) -> tuple[torch.Tensor | None, float]:
     """``(what is still to be added to the stream or None, its factor)`` of what a part or a block returned."""
+    if isinstance(pending, BranchSum):
+        return pending.materialize(), 1.0
     if pending is None or pending is ADDED:
         return None, 1.0
     if isinstance(pending, Scaled):
@@ -1352,4 +1367,24 @@ def branch_norm_sum(branches: list[torch.Tensor], weights: list[torch.Tensor], e
         ptrs += [_ptr(branches[i]), _ptr(weights[i])] if i < len(branches) else [None, None]
     code = _launch("llm_branch_norm_sum", *ptrs, len(branches), _ptr(out), n, c, float(eps), float(factor), _stream())
     _check(code, "branch_norm_sum")
+    return out
+
+
+def branch_sum_rmsnorm(pending: BranchSum, resid: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor | None:
+    """``resid += pending`` (see :class:`BranchSum`) in place, then ``resid * rsqrt(mean(resid^2) + eps) * weight`` in
+    ``out_dtype``, as one kernel.  None (nothing changed) where the rows do not fit its shared memory."""
+    n, c = resid.shape
+    _need(resid.dtype == torch.float32 and resid.is_contiguous() and weight.dtype == torch.float32 and weight.numel() == c, "branch_sum_rmsnorm: a float32 stream and norm weight")
+    for x, w in zip(pending.branches, pending.weights):
+        _need(x.dtype == torch.float32 and x.is_contiguous() and tuple(x.shape) == (n, c) and w.dtype == torch.float32 and w.numel() == c, "branch_sum_rmsnorm: branches are contiguous float32 of the stream's shape")
+    out = torch.empty((n, c), dtype=out_dtype, device=resid.device)
+    ptrs = []
+    for i in range(4):
+        ptrs += [_ptr(pending.branches[i]), _ptr(pending.weights[i])] if i < len(pending.branches) else [None, None]
+    code = _launch("llm_branch_sum_norm", *ptrs, len(pending.branches), _ptr(resid), _ptr(weight), _ptr(out), _code(out_dtype), n, c,
+                   pending.eps, pending.factor, float(eps), _stream())
+    if code == 10002:
+        add_launches(-1)
+        return None
+    _check(code, "branch_sum_rmsnorm")
     return out

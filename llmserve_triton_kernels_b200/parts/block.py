@@ -57,6 +57,10 @@ class PreNormBlock(Block):
             if pending.norm is not norm:
                 raise RuntimeError("a part handed the residual stream on normalised for another norm")
             return pending if getattr(consumer, "accepts_sink", False) else pending.materialize()
+        if isinstance(pending, ops.BranchSum) and hasattr(norm, "add_branches"):
+            x = norm.add_branches(resid, pending)  # the branches' meeting, the sum into the stream and the norm as one kernel
+            if x is not None:
+                return x
         delta, alpha = ops.split_pending(pending)
         if alpha != 1.0:
             return norm.add_forward(resid, delta, alpha=alpha)

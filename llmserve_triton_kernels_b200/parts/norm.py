@@ -46,6 +46,13 @@ class RMSNorm(Norm):
     def forward(self, x, rows=None):
         return self.add_forward(x, None, rows)
 
+    def add_branches(self, resid, pending):
+        """``resid += pending`` for a contribution that is still a list of branch outputs (``ops.BranchSum``), then the
+        norm, in one kernel where the norm is a plain RMS norm; None: the caller adds the contribution as a tensor."""
+        if self.groups != 1:
+            return None
+        return ops.branch_sum_rmsnorm(pending, resid, self.weight, self.eps, self.out_dtype)
+
     def add_forward(self, resid, delta, rows=None, alpha: float = 1.0):
         if self.groups == 1 and alpha == 1.0:
             return ops.rmsnorm(resid, self.weight, self.eps, delta=delta, rows=rows, out_dtype=self.out_dtype)

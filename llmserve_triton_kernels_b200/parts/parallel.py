@@ -82,7 +82,8 @@ class ParallelMixer(Mixer):
             else:
                 out = branch.forward(x, ctx, view)
             outs.append(out if out.dtype == torch.float32 else out.float())
-        return ops.branch_norm_sum(outs, self.out_weights, self.norm_eps, self.factor)
+        # still a list of branches: the norm behind this mixer may do the meeting, the sum into the stream and itself in one kernel
+        return ops.BranchSum(outs, self.out_weights, self.norm_eps, self.factor)
 
 
 register_part("mixer", "parallel", ParallelMixer)

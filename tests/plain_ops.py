@@ -414,7 +414,13 @@ def branch_norm_sum(branches, weights, eps, factor):
     return total * factor
 
 
+def branch_sum_rmsnorm(pending, resid, weight, eps, out_dtype):
+    resid.add_(branch_norm_sum(pending.branches, pending.weights, pending.eps, pending.factor))
+    return (resid * torch.rsqrt(resid.pow(2).mean(-1, keepdim=True) + eps) * weight).to(out_dtype)
+
+
 ALL = (
+    "branch_sum_rmsnorm",
     "qk_prepare",
     "sigmoid_attention",
     "retention_scan",

@@ -208,3 +208,21 @@ def test_branches_meet_normed_and_weighted():
     ws = [torch.randn(200, device=DEV) for _ in xs]
     for count in (1, 2, 3, 4):
         close(ops.branch_norm_sum(xs[:count], ws[:count], 1e-6, 1 / count), plain_ops.branch_norm_sum(xs[:count], ws[:count], 1e-6, 1 / count), 1e-5, f"{count} branches")
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_branches_meet_in_the_stream_and_are_normed(out_dtype):
+    ops = _ops()
+    torch.manual_seed(2)
+    for c in (200, 2048):
+        xs = [torch.randn(19, c, device=DEV) * s for s in (1, 5)]
+        ws = [torch.randn(c, device=DEV) for _ in xs]
+        wn = torch.randn(c, device=DEV)
+        r1 = torch.randn(19, c, device=DEV)
+        r2 = r1.clone()
+        pending = ops.BranchSum(xs, ws, 1e-6, 0.5)
+        a = ops.branch_sum_rmsnorm(pending, r1, wn, 1e-5, out_dtype)
+        b = plain_ops.branch_sum_rmsnorm(pending, r2, wn, 1e-5, out_dtype)
+        close(r1, r2, 1e-5, "the stream")
+        close(a, b, 1e-5 if out_dtype == torch.float32 else 1e-2, "the normed rows")
+        close(pending.materialize(), plain_ops.branch_norm_sum(xs, ws, 1e-6, 0.5), 1e-5, "as a tensor")
